@@ -1,0 +1,570 @@
+// Host side of libhl_b200: context, paged KV pool + TMA tensor maps, argument checks, launchers.
+// The C ABI is declared in include/hl_b200.h.  No CPU fallback: every entry point either queues
+// sm_100a kernels or returns an error status.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hl_b200.h"
+#include "attn_decode.cuh"
+#include "attn_prefill_mma.cuh"
+#include "attn_prefill_tc.cuh"
+#include "host_common.h"
+#include "kv_append.cuh"
+
+using namespace hl;
+
+// ---------------------------------------------------------------------------------------------
+// error plumbing
+// ---------------------------------------------------------------------------------------------
+int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...) {
+  if (ctx) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    ctx->err = buf;
+  }
+  return code;
+}
+
+#define HL_CUDA(ctx, expr)                                                                   \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess)                                                                   \
+      return hl_fail(ctx, HL_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                     __FILE__, __LINE__);                                                    \
+  } while (0)
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int32_t check_view(hl_ctx* ctx, const hl_view* v, const char* name) {
+  if (!v || !v->ptr) return hl_fail(ctx, HL_ERR_ARG, "%s: null view or pointer", name);
+  if (v->dtype != HL_DTYPE_F32 && v->dtype != HL_DTYPE_F16)
+    return hl_fail(ctx, HL_ERR_ARG, "%s: dtype %d is neither f32 nor f16", name, v->dtype);
+  const size_t el = v->dtype == HL_DTYPE_F16 ? 2 : 4;
+  if (reinterpret_cast<uintptr_t>(v->ptr) % el)
+    return hl_fail(ctx, HL_ERR_ALIGN, "%s: pointer not aligned to its element size", name);
+  return HL_OK;
+}
+
+View to_view(const hl_view* v) {
+  return View{v->ptr, v->dtype, v->tok_stride, v->head_stride, v->dim_stride};
+}
+
+int32_t check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_t layer) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!kv || !s) return hl_fail(ctx, HL_ERR_ARG, "null kv or shape");
+  if (layer < 0 || layer >= kv->n_layers)
+    return hl_fail(ctx, HL_ERR_ARG, "layer %d outside [0, %d)", layer, kv->n_layers);
+  if (s->n_head <= 0 || s->n_head_kv <= 0 || s->n_head % s->n_head_kv != 0)
+    return hl_fail(ctx, HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
+  if (s->n_head_kv != kv->n_head_kv || s->head_dim != kv->head_dim)
+    return hl_fail(ctx, HL_ERR_ARG, "shape (n_head_kv %d, head_dim %d) does not match the KV pool (%d, %d)",
+                   s->n_head_kv, s->head_dim, kv->n_head_kv, kv->head_dim);
+  if (s->head_dim != 64 && s->head_dim != 128)
+    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "head_dim %d: kernels are built for 64 and 128", s->head_dim);
+  if (s->rope_dim < 0 || s->rope_dim > s->head_dim || (s->rope_dim & 1))
+    return hl_fail(ctx, HL_ERR_ARG, "rope_dim %d must be even and <= head_dim", s->rope_dim);
+  if (s->rope_mode != HL_ROPE_INTERLEAVED && s->rope_mode != HL_ROPE_SPLIT_HALF)
+    return hl_fail(ctx, HL_ERR_ARG, "rope_mode %d unknown", s->rope_mode);
+  if (s->rope_dim > 0 && (!ctx->theta_d || ctx->theta_half < s->rope_dim / 2))
+    return hl_fail(ctx, HL_ERR_ARG, "RoPE table not set or shorter than rope_dim/2 (hl_b200_set_rope)");
+  return HL_OK;
+}
+
+}  // namespace
+
+int32_t hl_begin_timing(hl_ctx* ctx, float* gpu_ms) {
+  if (gpu_ms) HL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+  return HL_OK;
+}
+int32_t hl_end_timing(hl_ctx* ctx, float* gpu_ms) {
+  HL_CUDA(ctx, cudaGetLastError());
+  if (gpu_ms) {
+    HL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    HL_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+    HL_CUDA(ctx, cudaEventElapsedTime(gpu_ms, ctx->ev0, ctx->ev1));
+  }
+  return HL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------------------------
+extern "C" int32_t hl_b200_create(int32_t device, void* stream, hl_ctx** out) {
+  if (!out) return HL_ERR_ARG;
+  *out = nullptr;
+  int n_dev = 0;
+  if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) return HL_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return HL_ERR_CUDA;
+  if (prop.major != 10) return HL_ERR_UNSUPPORTED;  // sm_100a cubins only; there is no other path
+  if (cudaSetDevice(device) != cudaSuccess) return HL_ERR_CUDA;
+  hl_ctx* ctx = new hl_ctx();
+  ctx->device = device;
+  ctx->n_sm = prop.multiProcessorCount;
+  if (stream) {
+    ctx->stream = static_cast<cudaStream_t>(stream);
+  } else {
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+      delete ctx;
+      return HL_ERR_CUDA;
+    }
+    ctx->own_stream = true;
+  }
+  bool ok = cudaEventCreate(&ctx->ev0) == cudaSuccess && cudaEventCreate(&ctx->ev1) == cudaSuccess &&
+            cudaMalloc(&ctx->status_d, 2 * sizeof(int32_t)) == cudaSuccess &&
+            cudaMemset(ctx->status_d, 0, 2 * sizeof(int32_t)) == cudaSuccess;
+  cudaDriverEntryPointQueryResult qres;
+  void* fn = nullptr;
+  ok = ok && cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+                 cudaSuccess &&
+       fn != nullptr;
+  if (!ok) {
+    hl_b200_destroy(ctx);
+    return HL_ERR_CUDA;
+  }
+  ctx->encode_tiled = fn;
+  *out = ctx;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
+  if (!ctx) return HL_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->theta_d) cudaFree(ctx->theta_d);
+  if (ctx->status_d) cudaFree(ctx->status_d);
+  if (ctx->part_o) cudaFree(ctx->part_o);
+  if (ctx->part_ml) cudaFree(ctx->part_ml);
+  if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+  if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+  if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return HL_OK;
+}
+
+extern "C" const char* hl_b200_last_error(const hl_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+extern "C" int32_t hl_b200_sync(hl_ctx* ctx) {
+  if (!ctx) return HL_ERR_ARG;
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_set_stream(hl_ctx* ctx, void* stream) {
+  if (!ctx) return HL_ERR_ARG;
+  if (ctx->own_stream) {
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+    ctx->own_stream = false;
+  }
+  ctx->stream = static_cast<cudaStream_t>(stream);
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_device_status(hl_ctx* ctx, int32_t* code, int32_t* detail) {
+  if (!ctx || !code) return HL_ERR_ARG;
+  int32_t h[2] = {0, 0};
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  HL_CUDA(ctx, cudaMemcpy(h, ctx->status_d, sizeof h, cudaMemcpyDeviceToHost));
+  if (h[0] != 0) HL_CUDA(ctx, cudaMemset(ctx->status_d, 0, sizeof h));
+  *code = h[0];
+  if (detail) *detail = h[1];
+  if (h[0] != 0)
+    hl_fail(ctx, h[0], "device status %d (detail %d): %s", h[0], h[1],
+            h[0] == HL_ERR_TIMEOUT ? "a bounded wait gave up"
+                                   : "block table entry or position outside the KV pool");
+  return HL_OK;
+}
+
+extern "C" int64_t hl_b200_launch_count(const hl_ctx* ctx) { return ctx ? ctx->launches : -1; }
+
+extern "C" int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, int32_t prefill_kernel) {
+  if (!ctx) return HL_ERR_ARG;
+  if (decode_chunk_tokens < 0 || decode_chunk_tokens % 64 != 0)
+    return hl_fail(ctx, HL_ERR_ARG, "decode_chunk_tokens must be 0 or a multiple of 64");
+  if (prefill_kernel < 0 || prefill_kernel > 2) return hl_fail(ctx, HL_ERR_ARG, "prefill_kernel must be 0, 1 or 2");
+  ctx->decode_chunk = decode_chunk_tokens;
+  ctx->prefill_kernel = prefill_kernel;
+  return HL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE table
+// ---------------------------------------------------------------------------------------------
+extern "C" int32_t hl_b200_theta_table_h(float base, int32_t rope_dim, float* theta_h) {
+  if (!theta_h || rope_dim <= 0 || (rope_dim & 1) || !(base > 0.f)) return HL_ERR_ARG;
+  for (int i = 0; i < rope_dim / 2; ++i)
+    theta_h[i] = powf(1.0f / base, (2.0f * static_cast<float>(i)) / static_cast<float>(rope_dim));
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_theta_llama3_scale_h(float* theta_h, int32_t half, float factor,
+                                                float low_freq_factor, float high_freq_factor,
+                                                int32_t original_ctx) {
+  if (!theta_h || half <= 0 || !(factor > 0.f) || !(high_freq_factor > low_freq_factor) || original_ctx <= 0)
+    return HL_ERR_ARG;
+  const double two_pi = 6.283185307179586476925286766559;
+  const double low_wavelen = static_cast<double>(original_ctx) / low_freq_factor;
+  const double high_wavelen = static_cast<double>(original_ctx) / high_freq_factor;
+  for (int i = 0; i < half; ++i) {
+    const double th = theta_h[i];
+    const double wavelen = two_pi / th;
+    double r;
+    if (wavelen < high_wavelen) {
+      r = th;
+    } else if (wavelen > low_wavelen) {
+      r = th / factor;
+    } else {
+      const double smooth = (original_ctx / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor);
+      r = (1.0 - smooth) * th / factor + smooth * th;
+    }
+    theta_h[i] = static_cast<float>(r);
+  }
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_set_rope(hl_ctx* ctx, const float* theta_h, int32_t half) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!theta_h || half <= 0 || half > 128) return hl_fail(ctx, HL_ERR_ARG, "set_rope: bad table");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->theta_half < half) {
+    if (ctx->theta_d) cudaFree(ctx->theta_d);
+    ctx->theta_d = nullptr;
+    HL_CUDA(ctx, cudaMalloc(&ctx->theta_d, half * sizeof(float)));
+  }
+  ctx->theta_half = half;
+  HL_CUDA(ctx, cudaMemcpy(ctx->theta_d, theta_h, half * sizeof(float), cudaMemcpyHostToDevice));
+  return HL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// KV pool
+// ---------------------------------------------------------------------------------------------
+static int32_t make_map(hl_ctx* ctx, CUtensorMap* map, void* pool, uint64_t rows, int head_dim, int box_rows) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(head_dim), rows};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(head_dim) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pool, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return hl_fail(ctx, HL_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_head_kv, int32_t head_dim,
+                                     int32_t block_tokens, int32_t num_blocks, hl_kv** out) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!out) return hl_fail(ctx, HL_ERR_ARG, "kv_create: null out");
+  *out = nullptr;
+  if (n_layers <= 0 || n_head_kv <= 0 || num_blocks <= 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: non-positive size");
+  if (head_dim != 64 && head_dim != 128) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "kv_create: head_dim must be 64 or 128");
+  if (block_tokens <= 0 || block_tokens % 16 != 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: block_tokens must be a multiple of 16");
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * n_head_kv * block_tokens;
+  if (rows >= (1ull << 31)) return hl_fail(ctx, HL_ERR_CAPACITY, "kv_create: pool has too many rows for 32-bit TMA coordinates");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  hl_kv* kv = new hl_kv();
+  kv->n_layers = n_layers;
+  kv->n_head_kv = n_head_kv;
+  kv->head_dim = head_dim;
+  kv->block_tokens = block_tokens;
+  kv->num_blocks = num_blocks;
+  kv->bytes_each = rows * head_dim * 2;
+  kv->k.assign(n_layers, nullptr);
+  kv->v.assign(n_layers, nullptr);
+  kv->k_map.resize(n_layers);
+  kv->v_map.resize(n_layers);
+  kv->k_map128.resize(n_layers);
+  kv->v_map128.resize(n_layers);
+  for (int l = 0; l < n_layers; ++l) {
+    // Zero-filled so that rows of a partly filled block always hold finite values.
+    if (cudaMalloc(&kv->k[l], kv->bytes_each) != cudaSuccess || cudaMalloc(&kv->v[l], kv->bytes_each) != cudaSuccess ||
+        cudaMemsetAsync(kv->k[l], 0, kv->bytes_each, ctx->stream) != cudaSuccess ||
+        cudaMemsetAsync(kv->v[l], 0, kv->bytes_each, ctx->stream) != cudaSuccess) {
+      cudaGetLastError();
+      hl_b200_kv_destroy(ctx, kv);
+      return hl_fail(ctx, HL_ERR_CUDA, "kv_create: out of device memory at layer %d (%zu bytes per pool)", l, kv->bytes_each);
+    }
+    int32_t rc = make_map(ctx, &kv->k_map[l], kv->k[l], rows, head_dim, 16);
+    if (rc == HL_OK) rc = make_map(ctx, &kv->v_map[l], kv->v[l], rows, head_dim, 16);
+    // Wider boxes for the tcgen05 prefill kernel when a block holds a whole 128-key tile.
+    const int wide = block_tokens >= 128 && block_tokens % 128 == 0 ? 128 : 16;
+    if (rc == HL_OK) rc = make_map(ctx, &kv->k_map128[l], kv->k[l], rows, head_dim, wide);
+    if (rc == HL_OK) rc = make_map(ctx, &kv->v_map128[l], kv->v[l], rows, head_dim, wide);
+    if (rc != HL_OK) {
+      hl_b200_kv_destroy(ctx, kv);
+      return rc;
+    }
+  }
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  *out = kv;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_kv_destroy(hl_ctx* ctx, hl_kv* kv) {
+  if (!ctx || !kv) return HL_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto p : kv->k)
+    if (p) cudaFree(p);
+  for (auto p : kv->v)
+    if (p) cudaFree(p);
+  delete kv;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_kv_layer(const hl_kv* kv, int32_t layer, void** k_pool, void** v_pool, size_t* bytes_each) {
+  if (!kv || layer < 0 || layer >= kv->n_layers) return HL_ERR_ARG;
+  if (k_pool) *k_pool = kv->k[layer];
+  if (v_pool) *v_pool = kv->v[layer];
+  if (bytes_each) *bytes_each = kv->bytes_each;
+  return HL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// append
+// ---------------------------------------------------------------------------------------------
+static int32_t launch_append(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* k,
+                             const hl_view* v, int32_t n_tok, int32_t start_pos, int32_t batch_mode,
+                             const int32_t* ctx_lens, const int32_t* tables, int32_t max_blocks) {
+  int32_t rc = check_shape(ctx, kv, s, layer);
+  if (rc == HL_OK) rc = check_view(ctx, k, "k");
+  if (rc == HL_OK) rc = check_view(ctx, v, "v");
+  if (rc != HL_OK) return rc;
+  if (n_tok <= 0) return hl_fail(ctx, HL_ERR_ARG, "append requires at least one token");
+  if (!tables || max_blocks <= 0) return hl_fail(ctx, HL_ERR_ARG, "append: null or empty block table");
+  if (batch_mode && !ctx_lens) return hl_fail(ctx, HL_ERR_ARG, "append: null ctx_lens");
+  if (!batch_mode) {
+    if (start_pos < 0) return hl_fail(ctx, HL_ERR_ARG, "append: negative start_pos");
+    if (static_cast<int64_t>(start_pos) + n_tok > static_cast<int64_t>(max_blocks) * kv->block_tokens)
+      return hl_fail(ctx, HL_ERR_CAPACITY, "append exceeds KV cache capacity (%d + %d > %lld)", start_pos, n_tok,
+                     static_cast<long long>(max_blocks) * kv->block_tokens);
+  }
+  AppendArgs a{};
+  a.k = to_view(k);
+  a.v = to_view(v);
+  a.k_pool = kv->k[layer];
+  a.v_pool = kv->v[layer];
+  a.k_norm_w = s->k_norm_w;
+  a.theta = ctx->theta_d;
+  a.ctx_lens = ctx_lens;
+  a.block_tables = tables;
+  a.status = ctx->status_d;
+  a.eps = s->rms_eps;
+  a.n_tok = n_tok;
+  a.start_pos = start_pos;
+  a.batch_mode = batch_mode;
+  a.n_head_kv = s->n_head_kv;
+  a.rope_dim = s->rope_dim;
+  a.rope_mode = s->rope_mode;
+  a.block_tokens = kv->block_tokens;
+  a.num_blocks = kv->num_blocks;
+  a.max_blocks = max_blocks;
+  const int64_t rows = static_cast<int64_t>(n_tok) * s->n_head_kv;
+  const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (s->head_dim == 64)
+    kv_append_kernel<64><<<grid, 128, 0, ctx->stream>>>(a);
+  else
+    kv_append_kernel<128><<<grid, 128, 0, ctx->stream>>>(a);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_kv_append_seq(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                         const hl_view* k, const hl_view* v, int32_t n_tok, int32_t start_pos,
+                                         const int32_t* block_table, int32_t n_blocks_in_table) {
+  return launch_append(ctx, kv, layer, shape, k, v, n_tok, start_pos, 0, nullptr, block_table, n_blocks_in_table);
+}
+
+extern "C" int32_t hl_b200_kv_append_batch(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                           const hl_view* k, const hl_view* v, int32_t batch, const int32_t* ctx_lens,
+                                           const int32_t* block_tables, int32_t max_blocks_per_seq) {
+  return launch_append(ctx, kv, layer, shape, k, v, batch, 0, 1, ctx_lens, block_tables, max_blocks_per_seq);
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+static int32_t launch_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const DecodeArgs& a, int32_t batch) {
+  constexpr int NW = 4, STAGES = HD == 128 ? 3 : 4;
+  using Cfg = DecodeCfg<HD, NW, STAGES>;
+  auto kern = attn_decode_kernel<HD, NW, STAGES>;
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[ctx->device & 15] = true;
+  }
+  dim3 grid(a.max_chunks, a.n_head_kv, batch);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(kv->k_map[layer], kv->v_map[layer], a);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  if (a.max_chunks > 1) {
+    attn_combine_kernel<HD><<<dim3(a.n_head, batch), HD, 0, ctx->stream>>>(a);
+    ctx->launches++;
+    HL_CUDA(ctx, cudaGetLastError());
+  }
+  return HL_OK;
+}
+
+int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_kv, int32_t max_ctx) {
+  if (ctx->decode_chunk > 0) return ctx->decode_chunk;
+  // Aim at about eight CTAs per SM over the whole grid; never below one 64-token stage.
+  const int64_t base = static_cast<int64_t>(batch) * n_head_kv;
+  int64_t chunk = (static_cast<int64_t>(max_ctx) * base) / (8 * ctx->n_sm);
+  chunk = ((chunk + 63) / 64) * 64;
+  if (chunk < 64) chunk = 64;
+  if (chunk > 1024) chunk = 1024;
+  return static_cast<int32_t>(chunk);
+}
+
+extern "C" int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                       const hl_view* q, int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h,
+                                       const int32_t* block_tables, int32_t max_blocks_per_seq, const hl_view* out,
+                                       float* gpu_ms) {
+  int32_t rc = check_shape(ctx, kv, s, layer);
+  if (rc == HL_OK) rc = check_view(ctx, q, "q");
+  if (rc == HL_OK) rc = check_view(ctx, out, "out");
+  if (rc != HL_OK) return rc;
+  if (batch <= 0 || batch > 65535) return hl_fail(ctx, HL_ERR_ARG, "decode: batch %d outside [1, 65535]", batch);
+  if (!ctx_lens || !block_tables || max_blocks_per_seq <= 0) return hl_fail(ctx, HL_ERR_ARG, "decode: null ctx_lens or block table");
+  if (max_ctx_h <= 0) return hl_fail(ctx, HL_ERR_ARG, "decode: max_ctx_h must be positive");
+  if (static_cast<int64_t>(max_ctx_h) > static_cast<int64_t>(max_blocks_per_seq) * kv->block_tokens)
+    return hl_fail(ctx, HL_ERR_CAPACITY, "KV cache full: context %d exceeds the block table (%lld tokens)", max_ctx_h,
+                   static_cast<long long>(max_blocks_per_seq) * kv->block_tokens);
+  const int group = s->n_head / s->n_head_kv;
+  if (group > 16) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode: n_head / n_head_kv = %d > 16", group);
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+
+  DecodeArgs a{};
+  a.chunk_tokens = hl_decode_chunk_tokens(ctx, batch, s->n_head_kv, max_ctx_h);
+  a.max_chunks = (max_ctx_h + a.chunk_tokens - 1) / a.chunk_tokens;
+  if (a.max_chunks > 65535) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode: too many chunks");
+  if (a.max_chunks > 1) {
+    const size_t need = static_cast<size_t>(batch) * s->n_head * a.max_chunks;
+    if (need > ctx->part_cap) {  // grow-only scratch, like ensureActivationBuffers (naive.nim:241-262)
+      HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      if (ctx->part_o) cudaFree(ctx->part_o);
+      if (ctx->part_ml) cudaFree(ctx->part_ml);
+      ctx->part_o = ctx->part_ml = nullptr;
+      ctx->part_cap = 0;
+      HL_CUDA(ctx, cudaMalloc(&ctx->part_o, need * 128 * sizeof(float)));
+      HL_CUDA(ctx, cudaMalloc(&ctx->part_ml, need * 2 * sizeof(float)));
+      ctx->part_cap = need;
+    }
+  }
+  a.q = to_view(q);
+  a.out = to_view(out);
+  a.q_norm_w = s->q_norm_w;
+  a.theta = ctx->theta_d;
+  a.ctx_lens = ctx_lens;
+  a.block_tables = block_tables;
+  a.part_o = ctx->part_o;
+  a.part_ml = ctx->part_ml;
+  a.status = ctx->status_d;
+  a.eps = s->rms_eps;
+  a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(s->head_dim));
+  a.n_head = s->n_head;
+  a.n_head_kv = s->n_head_kv;
+  a.group = group;
+  a.rope_dim = s->rope_dim;
+  a.rope_mode = s->rope_mode;
+  a.block_tokens = kv->block_tokens;
+  a.num_blocks = kv->num_blocks;
+  a.max_blocks = max_blocks_per_seq;
+
+  rc = hl_begin_timing(ctx, gpu_ms);
+  if (rc != HL_OK) return rc;
+  rc = s->head_dim == 64 ? launch_decode<64>(ctx, kv, layer, a, batch) : launch_decode<128>(ctx, kv, layer, a, batch);
+  if (rc != HL_OK) return rc;
+  return hl_end_timing(ctx, gpu_ms);
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+static int32_t launch_prefill_mma(hl_ctx* ctx, hl_kv* kv, int32_t layer, const PrefillArgs& a) {
+  constexpr int NW = 8, STAGES = 2;
+  using Cfg = PrefillMmaCfg<HD, NW, STAGES>;
+  auto kern = attn_prefill_mma_kernel<HD, NW, STAGES>;
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[ctx->device & 15] = true;
+  }
+  dim3 grid((a.n_tok + Cfg::kBM - 1) / Cfg::kBM, a.n_head);
+  kern<<<grid, (NW + 1) * 32, Cfg::kSmemBytes, ctx->stream>>>(kv->k_map[layer], kv->v_map[layer], a);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                        const hl_view* q, int32_t n_tok, int32_t start_pos, const int32_t* block_table,
+                                        int32_t n_blocks_in_table, const hl_view* out, float* gpu_ms) {
+  int32_t rc = check_shape(ctx, kv, s, layer);
+  if (rc == HL_OK) rc = check_view(ctx, q, "q");
+  if (rc == HL_OK) rc = check_view(ctx, out, "out");
+  if (rc != HL_OK) return rc;
+  if (n_tok <= 0) return hl_fail(ctx, HL_ERR_ARG, "prefill requires at least one token");
+  if (start_pos < 0) return hl_fail(ctx, HL_ERR_ARG, "prefill: negative start_pos");
+  if (!block_table || n_blocks_in_table <= 0) return hl_fail(ctx, HL_ERR_ARG, "prefill: null or empty block table");
+  if (static_cast<int64_t>(start_pos) + n_tok > static_cast<int64_t>(n_blocks_in_table) * kv->block_tokens)
+    return hl_fail(ctx, HL_ERR_CAPACITY, "prefill exceeds KV cache capacity (%d + %d > %lld)", start_pos, n_tok,
+                   static_cast<long long>(n_blocks_in_table) * kv->block_tokens);
+  if (s->n_head > 65535) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: too many heads");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+
+  PrefillArgs a{};
+  a.q = to_view(q);
+  a.out = to_view(out);
+  a.q_norm_w = s->q_norm_w;
+  a.theta = ctx->theta_d;
+  a.block_table = block_table;
+  a.status = ctx->status_d;
+  a.eps = s->rms_eps;
+  a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(s->head_dim));
+  a.n_tok = n_tok;
+  a.start_pos = start_pos;
+  a.n_head = s->n_head;
+  a.n_head_kv = s->n_head_kv;
+  a.group = s->n_head / s->n_head_kv;
+  a.rope_dim = s->rope_dim;
+  a.rope_mode = s->rope_mode;
+  a.block_tokens = kv->block_tokens;
+  a.num_blocks = kv->num_blocks;
+  a.n_blocks_in_table = n_blocks_in_table;
+
+  rc = hl_begin_timing(ctx, gpu_ms);
+  if (rc != HL_OK) return rc;
+  const bool want_tc = ctx->prefill_kernel == 2 || (ctx->prefill_kernel == 0 && hl_prefill_tc_default(a, s->head_dim));
+  if (want_tc) {
+    if (!hl_prefill_tc_supported(a, s->head_dim))
+      return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: the tcgen05 kernel does not take this shape");
+    rc = hl_launch_prefill_tc(ctx, kv, layer, a, s->head_dim);
+  } else {
+    rc = s->head_dim == 64 ? launch_prefill_mma<64>(ctx, kv, layer, a) : launch_prefill_mma<128>(ctx, kv, layer, a);
+  }
+  if (rc != HL_OK) return rc;
+  return hl_end_timing(ctx, gpu_ms);
+}

@@ -1,0 +1,40 @@
+// Host-side objects behind the opaque handles of include/hl_b200.h.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hl_b200.h"
+
+struct hl_ctx {
+  int device = 0;
+  int n_sm = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float* theta_d = nullptr;  // RoPE theta table [theta_half]
+  int theta_half = 0;
+  int32_t* status_d = nullptr;  // {code, detail} written by bounded waits / bounds checks
+  float* part_o = nullptr;      // split-KV partial outputs (grow-only scratch)
+  float* part_ml = nullptr;     // split-KV partial (max, sum)
+  size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
+  void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved through the runtime
+  int32_t decode_chunk = 0;
+  int32_t prefill_kernel = 0;
+  int64_t launches = 0;
+  std::string err;
+};
+
+struct hl_kv {
+  int n_layers = 0, n_head_kv = 0, head_dim = 0, block_tokens = 0, num_blocks = 0;
+  size_t bytes_each = 0;
+  std::vector<__half*> k, v;                 // per layer pools
+  std::vector<CUtensorMap> k_map, v_map;     // 16-row x 64-column boxes, 128-byte swizzle
+  std::vector<CUtensorMap> k_map128, v_map128;  // 128-row boxes when a block holds >= 128 tokens
+};
+
+int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...);

@@ -1,0 +1,204 @@
+"""Thin Python host layer over the C ABI: device buffers come from torch, compute from the .so.
+
+Each method maps 1:1 to an entry point of ``include/hl_b200.h``; a non-zero status becomes a
+``HlError`` (a ``ValueError``, the exception type the reference backends raise for bad shapes
+and full caches, src/hippo_leap/backends/naive.nim:3969-3976, 4594-4599).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+
+class HlError(ValueError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{L.STATUS_NAMES.get(code, code)}: {msg}")
+        self.code = code
+
+
+def theta_table(rope_dim: int, base: float) -> np.ndarray:
+    """theta_i = powf(1/base, 2i/rope_dim) on the host (naive.nim:3850-3855)."""
+    th = np.empty(rope_dim // 2, np.float32)
+    rc = L.load().hl_b200_theta_table_h(base, rope_dim, th.ctypes.data_as(C.POINTER(C.c_float)))
+    if rc != 0:
+        raise HlError(rc, "theta_table: bad rope_dim or base")
+    return th
+
+
+def theta_llama3_scale(theta: np.ndarray, factor: float = 32.0, low_freq_factor: float = 1.0,
+                       high_freq_factor: float = 4.0, original_ctx: int = 8192) -> np.ndarray:
+    th = np.ascontiguousarray(theta, np.float32).copy()
+    rc = L.load().hl_b200_theta_llama3_scale_h(th.ctypes.data_as(C.POINTER(C.c_float)), th.size,
+                                               factor, low_freq_factor, high_freq_factor,
+                                               original_ctx)
+    if rc != 0:
+        raise HlError(rc, "theta_llama3_scale: bad arguments")
+    return th
+
+
+@dataclass
+class AttnShape:
+    n_head: int
+    n_head_kv: int
+    head_dim: int
+    rope_dim: int | None = None
+    rope_mode: int = L.HL_ROPE_SPLIT_HALF
+    rms_eps: float = 1e-6
+    q_norm_w: torch.Tensor | None = None  # device float32 [head_dim]
+    k_norm_w: torch.Tensor | None = None
+
+    def c(self) -> L.AttnShapeC:
+        for w in (self.q_norm_w, self.k_norm_w):
+            if w is not None:
+                assert w.is_cuda and w.dtype == torch.float32 and w.is_contiguous()
+                assert w.numel() == self.head_dim
+        return L.AttnShapeC(
+            self.n_head, self.n_head_kv, self.head_dim,
+            self.head_dim if self.rope_dim is None else self.rope_dim, self.rope_mode,
+            self.rms_eps,
+            None if self.q_norm_w is None else self.q_norm_w.data_ptr(),
+            None if self.k_norm_w is None else self.k_norm_w.data_ptr())
+
+
+def view_of(t: torch.Tensor) -> L.ViewC:
+    """[n_tok, heads, head_dim] tensor (any strides, float32 or float16) -> hl_view."""
+    assert t.is_cuda and t.dim() == 3, "expected a CUDA tensor shaped [n_tok, heads, head_dim]"
+    if t.dtype == torch.float32:
+        dt = L.HL_DTYPE_F32
+    elif t.dtype == torch.float16:
+        dt = L.HL_DTYPE_F16
+    else:
+        raise HlError(L.HL_ERR_ARG, f"dtype {t.dtype} is neither float32 nor float16")
+    s = t.stride()
+    return L.ViewC(t.data_ptr(), dt, s[0], s[1], s[2])
+
+
+def _i32_dev(t: torch.Tensor) -> int:
+    assert t.is_cuda and t.dtype == torch.int32 and t.is_contiguous()
+    return t.data_ptr()
+
+
+class KvPool:
+    """Paged fp16 KV cache: per layer K and V pools [num_blocks, n_head_kv, block_tokens, hd]."""
+
+    def __init__(self, ctx: "Context", handle, n_layers, n_head_kv, head_dim, block_tokens,
+                 num_blocks):
+        self.ctx, self.handle = ctx, handle
+        self.n_layers, self.n_head_kv, self.head_dim = n_layers, n_head_kv, head_dim
+        self.block_tokens, self.num_blocks = block_tokens, num_blocks
+
+    def layer_ptrs(self, layer: int):
+        k, v, n = C.c_void_p(), C.c_void_p(), C.c_size_t()
+        rc = self.ctx.lib.hl_b200_kv_layer(self.handle, layer, C.byref(k), C.byref(v), C.byref(n))
+        if rc != 0:
+            raise HlError(rc, "kv_layer: bad layer")
+        return k.value, v.value, n.value
+
+    def destroy(self):
+        if self.handle is not None and self.ctx.handle is not None:
+            self.ctx.lib.hl_b200_kv_destroy(self.ctx.handle, self.handle)
+        self.handle = None
+
+
+class Context:
+    """One per process and device (hl_ctx).  Not re-entrant."""
+
+    def __init__(self, device: int = 0, stream: torch.cuda.Stream | None = None):
+        self.lib = L.load()
+        self.device = device
+        h = C.c_void_p()
+        sp = None if stream is None else C.c_void_p(stream.cuda_stream)
+        rc = self.lib.hl_b200_create(device, sp, C.byref(h))
+        if rc != 0:
+            raise HlError(rc, f"hl_b200_create(device={device}) failed: no usable sm_100 GPU "
+                              "(this library has no CPU fallback)")
+        self.handle = h
+        self._stream = stream
+
+    # -- plumbing ---------------------------------------------------------------------------
+    def _check(self, rc: int):
+        if rc != 0:
+            raise HlError(rc, self.lib.hl_b200_last_error(self.handle).decode())
+
+    def close(self):
+        if self.handle is not None:
+            self.lib.hl_b200_destroy(self.handle)
+            self.handle = None
+
+    def sync(self):
+        self._check(self.lib.hl_b200_sync(self.handle))
+
+    def set_stream(self, stream: torch.cuda.Stream):
+        self._check(self.lib.hl_b200_set_stream(self.handle, C.c_void_p(stream.cuda_stream)))
+        self._stream = stream
+
+    def device_status(self):
+        code, detail = C.c_int32(), C.c_int32()
+        self._check(self.lib.hl_b200_device_status(self.handle, C.byref(code), C.byref(detail)))
+        return code.value, detail.value
+
+    def launch_count(self) -> int:
+        return self.lib.hl_b200_launch_count(self.handle)
+
+    def set_tuning(self, decode_chunk_tokens: int = 0, prefill_kernel: int = 0):
+        self._check(self.lib.hl_b200_set_tuning(self.handle, decode_chunk_tokens, prefill_kernel))
+
+    # -- rope / kv ---------------------------------------------------------------------------
+    def set_rope(self, theta: np.ndarray):
+        th = np.ascontiguousarray(theta, np.float32)
+        self._check(self.lib.hl_b200_set_rope(self.handle, th.ctypes.data_as(C.POINTER(C.c_float)),
+                                              th.size))
+
+    def kv_create(self, n_layers, n_head_kv, head_dim, block_tokens, num_blocks) -> KvPool:
+        h = C.c_void_p()
+        self._check(self.lib.hl_b200_kv_create(self.handle, n_layers, n_head_kv, head_dim,
+                                               block_tokens, num_blocks, C.byref(h)))
+        return KvPool(self, h, n_layers, n_head_kv, head_dim, block_tokens, num_blocks)
+
+    def kv_append_seq(self, kv: KvPool, layer: int, shape: AttnShape, k, v, start_pos: int,
+                      block_table: torch.Tensor):
+        sc, kc, vc = shape.c(), view_of(k), view_of(v)
+        self._check(self.lib.hl_b200_kv_append_seq(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(kc), C.byref(vc), k.shape[0],
+            start_pos, _i32_dev(block_table), block_table.numel()))
+
+    def kv_append_batch(self, kv: KvPool, layer: int, shape: AttnShape, k, v,
+                        ctx_lens: torch.Tensor, block_tables: torch.Tensor):
+        sc, kc, vc = shape.c(), view_of(k), view_of(v)
+        self._check(self.lib.hl_b200_kv_append_batch(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(kc), C.byref(vc), k.shape[0],
+            _i32_dev(ctx_lens), _i32_dev(block_tables), block_tables.shape[1]))
+
+    # -- attention ---------------------------------------------------------------------------
+    def attn_prefill(self, kv: KvPool, layer: int, shape: AttnShape, q, start_pos: int,
+                     block_table: torch.Tensor, out: torch.Tensor | None = None,
+                     timed: bool = False):
+        if out is None:
+            out = torch.empty((q.shape[0], shape.n_head, shape.head_dim), dtype=torch.float32,
+                              device=q.device)
+        sc, qc, oc = shape.c(), view_of(q), view_of(out)
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_attn_prefill(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], start_pos,
+            _i32_dev(block_table), block_table.numel(), C.byref(oc),
+            C.byref(ms) if timed else None))
+        return (out, ms.value) if timed else out
+
+    def attn_decode(self, kv: KvPool, layer: int, shape: AttnShape, q, ctx_lens: torch.Tensor,
+                    max_ctx: int, block_tables: torch.Tensor, out: torch.Tensor | None = None,
+                    timed: bool = False):
+        if out is None:
+            out = torch.empty((q.shape[0], shape.n_head, shape.head_dim), dtype=torch.float32,
+                              device=q.device)
+        sc, qc, oc = shape.c(), view_of(q), view_of(out)
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_attn_decode(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0],
+            _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
+            C.byref(oc), C.byref(ms) if timed else None))
+        return (out, ms.value) if timed else out

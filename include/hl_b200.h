@@ -1,0 +1,165 @@
+/*
+ * libhl_b200 -- C ABI of the B200 (sm_100a) attention hot path for hippo_leap.
+ *
+ * This is the boundary a `-d:backendB200` build of hippo_leap binds with `importc`
+ * (src/hippo_leap/backends/b200.nim): RoPE (+ optional per-head QK RMSNorm), KV-cache
+ * append, causal grouped-query attention for prefill and single-token attention over the
+ * KV cache for decode.  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Conventions
+ *  - Every entry point returns an hl_status (0 = ok).  Nothing throws, aborts or exits.
+ *    hl_b200_last_error(ctx) gives the text of the last failure on that context.
+ *  - Pointers are DEVICE pointers unless the name ends in _h (host).
+ *  - Work is queued on the context's stream and NOT synchronised unless `gpu_ms` is
+ *    non-NULL (then the call brackets its kernels with events, synchronises, and returns
+ *    the device time in milliseconds) or hl_b200_sync() is called.
+ *  - A context is not re-entrant: one thread at a time per context (the reference
+ *    serialises callers with InferenceContext.lock, src/hippo_leap/inference.nim:53-54).
+ *  - No CPU fallback exists.  Without a usable sm_100 device hl_b200_create fails.
+ */
+#ifndef HL_B200_H_
+#define HL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hl_status {
+  HL_OK = 0,
+  HL_ERR_ARG = 1,         /* null / negative / inconsistent argument            */
+  HL_ERR_CAPACITY = 2,    /* position or block index beyond the KV pool         */
+  HL_ERR_ALIGN = 3,       /* pointer or stride breaks an alignment rule         */
+  HL_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed                */
+  HL_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up                 */
+  HL_ERR_BOUNDS = 6,      /* a device-side index check failed (block table)     */
+  HL_ERR_UNSUPPORTED = 7  /* shape outside what the kernels are built for       */
+} hl_status;
+
+enum { HL_DTYPE_F32 = 0, HL_DTYPE_F16 = 1 };
+
+/* RoPE pairing.  INTERLEAVED rotates (2i, 2i+1) like the CPU op
+ * (src/hippo_leap/tensor.nim:156-166); SPLIT_HALF rotates (i, i+ropeDim/2) like every
+ * reference GPU kernel (src/hippo_leap/backends/naive.nim:3025-3030), which is what the
+ * drop-in backend must use for an unchanged greedy token stream. */
+enum { HL_ROPE_INTERLEAVED = 0, HL_ROPE_SPLIT_HALF = 1 };
+
+typedef struct hl_ctx hl_ctx; /* one per process and device: stream, theta table, scratch */
+typedef struct hl_kv hl_kv;   /* paged fp16 KV pool for all layers of one model          */
+
+/* Shape of the attention op; the fields come from HParams (src/hippo_leap/model.nim:24-50). */
+typedef struct hl_attn_shape {
+  int32_t n_head;      /* query heads                                       */
+  int32_t n_head_kv;   /* KV heads; n_head % n_head_kv == 0                 */
+  int32_t head_dim;    /* 64 or 128                                         */
+  int32_t rope_dim;    /* even, <= head_dim; dims >= rope_dim not rotated   */
+  int32_t rope_mode;   /* HL_ROPE_*                                         */
+  float rms_eps;       /* eps of the QK RMSNorm (hp.rmsEps)                 */
+  const float* q_norm_w; /* device [head_dim] or NULL: attn_q_norm.weight   */
+  const float* k_norm_w; /* device [head_dim] or NULL: attn_k_norm.weight   */
+} hl_attn_shape;
+
+/* Strided view of a [n_tok][heads][head_dim] activation.  Strides are in ELEMENTS.
+ * The reference's `[dim, S]` buffers (element (r, t) at r*S + t,
+ * src/hippo_leap/backends/naive.nim:2984-2990) are {tok 1, head head_dim*S, dim S};
+ * token-major buffers are {tok heads*head_dim, head head_dim, dim 1}. */
+typedef struct hl_view {
+  void* ptr;
+  int32_t dtype; /* HL_DTYPE_* */
+  int64_t tok_stride, head_stride, dim_stride;
+} hl_view;
+
+/* ---- context ---------------------------------------------------------------------- */
+
+/* Replaces ensureGpuContext (src/hippo_leap/backends/naive.nim:237-262): binds `device`,
+ * checks it is compute capability 10.x, adopts `stream` (a cudaStream_t) or creates one
+ * when `stream` is NULL. */
+int32_t hl_b200_create(int32_t device, void* stream, hl_ctx** out);
+/* Replaces unloadModelBackend (naive.nim:3960-3962): frees everything the context owns. */
+int32_t hl_b200_destroy(hl_ctx* ctx);
+const char* hl_b200_last_error(const hl_ctx* ctx);
+int32_t hl_b200_sync(hl_ctx* ctx);
+/* Adopt another stream (e.g. the caller framework's current stream). */
+int32_t hl_b200_set_stream(hl_ctx* ctx, void* stream);
+/* Reads and clears the device status word that bounded waits and block-table checks set. */
+int32_t hl_b200_device_status(hl_ctx* ctx, int32_t* code, int32_t* detail);
+/* Number of kernels this context has launched since creation (for launch accounting). */
+int64_t hl_b200_launch_count(const hl_ctx* ctx);
+
+/* ---- RoPE table ------------------------------------------------------------------- */
+
+/* Host helper: theta_i = powf(1/base, 2i/rope_dim), i < rope_dim/2 -- the table
+ * ensureModelGpuPtrs builds (naive.nim:3850-3855). */
+int32_t hl_b200_theta_table_h(float base, int32_t rope_dim, float* theta_h);
+/* Host helper: the published "llama3" frequency scaling applied in place to a theta table
+ * (no counterpart in the reference; a host-side transform of the table). */
+int32_t hl_b200_theta_llama3_scale_h(float* theta_h, int32_t half, float factor,
+                                     float low_freq_factor, float high_freq_factor,
+                                     int32_t original_ctx);
+/* Uploads theta[half] (replaces the upload at naive.nim:3856-3861). */
+int32_t hl_b200_set_rope(hl_ctx* ctx, const float* theta_h, int32_t half);
+
+/* ---- KV cache ---------------------------------------------------------------------
+ * Replaces initGpuKvCache (naive.nim:3552-3567).  Per layer one K pool and one V pool,
+ * fp16, laid out [num_blocks][n_head_kv][block_tokens][head_dim]: a (block, kv-head) tile is
+ * one contiguous run of block_tokens rows of head_dim*2 bytes (128 or 256 B, so every row is
+ * 128-byte aligned).  K is stored after QK-norm and RoPE, V raw, as in the reference.
+ * block_tokens must be a multiple of 16.  A block table maps a sequence's logical block
+ * (position / block_tokens) to a physical block: int32 [n_seq][max_blocks_per_seq]. */
+int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_head_kv, int32_t head_dim,
+                          int32_t block_tokens, int32_t num_blocks, hl_kv** out);
+int32_t hl_b200_kv_destroy(hl_ctx* ctx, hl_kv* kv);
+/* Device pointers and size in bytes of one layer's pools (to fill GpuKvCache.k/v[layer],
+ * src/hippo_leap/backend_types.nim:28-34). */
+int32_t hl_b200_kv_layer(const hl_kv* kv, int32_t layer, void** k_pool, void** v_pool,
+                         size_t* bytes_each);
+
+/* Replaces gpuQkNormPrefill(K) + gpuRopeAtPos(K) + gpuStoreKV(K), gpuStoreKV(V)
+ * (naive.nim:4070-4076) for ONE sequence: n_tok tokens at positions start_pos.. of the
+ * sequence whose block table (device, int32[n_blocks_in_table]) is given. */
+int32_t hl_b200_kv_append_seq(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                              const hl_view* k, const hl_view* v, int32_t n_tok,
+                              int32_t start_pos, const int32_t* block_table,
+                              int32_t n_blocks_in_table);
+/* Replaces gpuQkNorm(K) + the K half of gpuRopeQKDecode + gpuStoreKVPair, or
+ * gpuFusedRopeStoreKV (naive.nim:4699-4710, 5186-5190) for a BATCH of sequences: token i
+ * belongs to sequence i and is stored at position ctx_lens[i] - 1. */
+int32_t hl_b200_kv_append_batch(hl_ctx* ctx, hl_kv* kv, int32_t layer,
+                                const hl_attn_shape* shape, const hl_view* k, const hl_view* v,
+                                int32_t batch, const int32_t* ctx_lens,
+                                const int32_t* block_tables, int32_t max_blocks_per_seq);
+
+/* ---- attention --------------------------------------------------------------------- */
+
+/* Replaces gpuQkNormPrefill(Q) + gpuRopeAtPos(Q) + gpuAttentionPrefill
+ * (naive.nim:4067-4078): for query token t (position start_pos + t) and head h,
+ * out[t,h,:] = softmax_j((q.k_j)/sqrt(head_dim)) . v_j over keys j <= start_pos + t of KV
+ * head h / (n_head / n_head_kv).  Q is normed, rotated and scaled inside the kernel; K/V
+ * are read from the paged cache (append them first).  out: fp32 or fp16 view.
+ * No 4096-key cap (naive.nim:3404) and start_pos may be non-zero. */
+int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                             const hl_view* q, int32_t n_tok, int32_t start_pos,
+                             const int32_t* block_table, int32_t n_blocks_in_table,
+                             const hl_view* out, float* gpu_ms);
+
+/* Replaces gpuQkNorm(Q) + the Q half of gpuRopeQKDecode + gpuAttentionDecode
+ * (naive.nim:4697-4717): one query token per sequence, sequence i attending its first
+ * ctx_lens[i] cached keys (the new token's own K/V included: curLen = pos + 1).
+ * Split-KV: the context is cut into chunks that run in parallel and a second pass merges
+ * the partial (max, sum, out) triples.  max_ctx_h >= max_i ctx_lens[i] (host value, sizes
+ * the grid and the scratch). */
+int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                            const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                            int32_t max_ctx_h, const int32_t* block_tables,
+                            int32_t max_blocks_per_seq, const hl_view* out, float* gpu_ms);
+
+/* Tunables (0 = automatic): tokens per split-KV chunk for decode; which prefill kernel
+ * runs (0 auto, 1 = warp-MMA kernel, 2 = tcgen05 kernel). */
+int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, int32_t prefill_kernel);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HL_B200_H_ */

@@ -1,0 +1,102 @@
+"""GPU parity of the CUDA path (through the C ABI) against the CPU oracle, on small seeded cases."""
+import numpy as np
+import pytest
+import torch
+
+import hippo_leap_b200 as hl
+from tests.helpers import assert_parity, oracle_seq, permuted_table
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(hl_ctx, n_head, n_head_kv, hd, S_total, bt, rope_mode, norm, seed, base=1e4):
+    g = np.random.Generator(np.random.PCG64(seed))
+    theta = hl.theta_table(hd, base)
+    hl_ctx.set_rope(theta)
+    qw = kw = None
+    if norm:
+        qw = g.uniform(0.9, 1.1, hd).astype(np.float32)
+        kw = g.uniform(0.9, 1.1, hd).astype(np.float32)
+    shape = hl.AttnShape(n_head, n_head_kv, hd, hd, rope_mode, 1e-6,
+                         None if qw is None else torch.from_numpy(qw).cuda(),
+                         None if kw is None else torch.from_numpy(kw).cuda())
+    n_blocks = (S_total + bt - 1) // bt
+    num_blocks = n_blocks + 7
+    table = permuted_table(n_blocks, num_blocks, seed)
+    kv = hl_ctx.kv_create(1, n_head_kv, hd, bt, num_blocks)
+    return g, theta, qw, kw, shape, kv, table
+
+
+@pytest.mark.parametrize("hd,n_head,n_head_kv,S,bt,rope_mode,norm", [
+    (64, 32, 4, 128, 16, hl.HL_ROPE_INTERLEAVED, False),   # config 1 prefill
+    (64, 32, 4, 128, 16, hl.HL_ROPE_SPLIT_HALF, False),
+    (128, 8, 2, 200, 16, hl.HL_ROPE_SPLIT_HALF, True),
+    (128, 4, 4, 1, 16, hl.HL_ROPE_INTERLEAVED, False),
+    (64, 4, 1, 17, 32, hl.HL_ROPE_INTERLEAVED, True),
+    (128, 8, 1, 257, 64, hl.HL_ROPE_SPLIT_HALF, False),
+    (128, 4, 2, 513, 128, hl.HL_ROPE_INTERLEAVED, False),
+])
+def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm):
+    g, theta, qw, kw, shape, kv, table = _setup(hl_ctx, n_head, n_head_kv, hd, S, bt, rope_mode, norm, 11)
+    q = g.standard_normal((S, n_head, hd), dtype=np.float32)
+    k = g.standard_normal((S, n_head_kv, hd), dtype=np.float32)
+    v = g.standard_normal((S, n_head_kv, hd), dtype=np.float32)
+    tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    tt = torch.from_numpy(table).cuda()
+    hl_ctx.set_tuning(0, 1)
+    hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
+    out = hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt)
+    got = out.cpu().numpy()
+    want = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw)
+    want16 = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw, kv_fp16=True)
+    assert_parity(got, want, "prefill vs fp32 oracle")
+    assert_parity(got, want16, "prefill vs fp16-KV oracle", 1e-3, 6e-4)
+    kv.destroy()
+
+
+@pytest.mark.parametrize("hd,n_head,n_head_kv,bt,rope_mode,norm,ctxs,chunk", [
+    (64, 32, 4, 16, hl.HL_ROPE_INTERLEAVED, False, [129], 0),          # config 1 first decode step
+    (128, 32, 8, 16, hl.HL_ROPE_SPLIT_HALF, False, [1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, 257, 700], 0),
+    (128, 32, 8, 16, hl.HL_ROPE_SPLIT_HALF, True, [300, 1, 1000, 64], 64),
+    (128, 8, 8, 32, hl.HL_ROPE_INTERLEAVED, False, [513, 77], 128),
+    (64, 16, 1, 16, hl.HL_ROPE_SPLIT_HALF, True, [90, 200, 333], 0),
+])
+def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs, chunk):
+    ctxs = np.asarray(ctxs, np.int32)
+    B = len(ctxs)
+    g, theta, qw, kw, shape, _kv, _ = _setup(hl_ctx, n_head, n_head_kv, hd, 16, bt, rope_mode, norm, 23)
+    _kv.destroy()
+    need = (ctxs + bt - 1) // bt
+    num_blocks = int(need.sum()) + 5
+    perm = g.permutation(num_blocks).astype(np.int32)
+    tables = np.full((B, int(need.max())), -1, np.int32)
+    o = 0
+    for i, n in enumerate(need):
+        tables[i, :n] = perm[o:o + n]
+        o += int(n)
+    kv = hl_ctx.kv_create(1, n_head_kv, hd, bt, num_blocks)
+    ttab = torch.from_numpy(tables).cuda()
+    want = np.zeros((B, n_head, hd), np.float32)
+    want16 = np.zeros_like(want)
+    qn = g.standard_normal((B, n_head, hd), dtype=np.float32)
+    kn = g.standard_normal((B, n_head_kv, hd), dtype=np.float32)
+    vn = g.standard_normal((B, n_head_kv, hd), dtype=np.float32)
+    for i, c in enumerate(ctxs):
+        kp = g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32)
+        vp = g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32)
+        if c > 1:
+            hl_ctx.kv_append_seq(kv, 0, shape, torch.from_numpy(kp).cuda(), torch.from_numpy(vp).cuda(), 0,
+                                 ttab[i, :need[i]].contiguous())
+        for fp16, dst in ((False, want), (True, want16)):
+            dst[i] = oracle_seq(qn[i:i + 1], kn[i:i + 1], vn[i:i + 1], theta=theta, rope_mode=rope_mode,
+                                q_norm_w=qw, k_norm_w=kw, kv_fp16=fp16,
+                                prefix=(kp, vp) if c > 1 else None)[0]
+    tctx = torch.from_numpy(ctxs).cuda()
+    hl_ctx.set_tuning(chunk, 1)
+    hl_ctx.kv_append_batch(kv, 0, shape, torch.from_numpy(kn).cuda(), torch.from_numpy(vn).cuda(), tctx, ttab)
+    out = hl_ctx.attn_decode(kv, 0, shape, torch.from_numpy(qn).cuda(), tctx, int(ctxs.max()), ttab)
+    got = out.cpu().numpy()
+    hl_ctx.set_tuning(0, 1)
+    assert_parity(got, want, "decode vs fp32 oracle")
+    assert_parity(got, want16, "decode vs fp16-KV oracle", 1e-3, 6e-4)
+    kv.destroy()
