@@ -112,13 +112,16 @@ class Context:
         self.lib = L.load()
         self.device = device
         h = C.c_void_p()
-        sp = None if stream is None else C.c_void_p(stream.cuda_stream)
-        rc = self.lib.hl_b200_create(device, sp, C.byref(h))
+        rc = self.lib.hl_b200_create(device, None, C.byref(h))
         if rc != 0:
             raise HlError(rc, f"hl_b200_create(device={device}) failed: no usable sm_100 GPU "
                               "(this library has no CPU fallback)")
         self.handle = h
-        self._stream = stream
+        self._stream = None
+        if stream is not None:
+            # torch's default stream has handle 0, which hl_b200_create reads as "make your
+            # own stream"; set_stream adopts handle 0 as the legacy default stream.
+            self.set_stream(stream)
 
     # -- plumbing ---------------------------------------------------------------------------
     def _check(self, rc: int):

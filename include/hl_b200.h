@@ -81,7 +81,8 @@ int32_t hl_b200_create(int32_t device, void* stream, hl_ctx** out);
 int32_t hl_b200_destroy(hl_ctx* ctx);
 const char* hl_b200_last_error(const hl_ctx* ctx);
 int32_t hl_b200_sync(hl_ctx* ctx);
-/* Adopt another stream (e.g. the caller framework's current stream). */
+/* Adopt another stream (e.g. the caller framework's current stream).  Here NULL means the
+ * legacy default stream (handle 0), not "create one". */
 int32_t hl_b200_set_stream(hl_ctx* ctx, void* stream);
 /* Reads and clears the device status word that bounded waits and block-table checks set. */
 int32_t hl_b200_device_status(hl_ctx* ctx, int32_t* code, int32_t* detail);
