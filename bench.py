@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+Headline workload (one "step"): one decode step of the batched-decode configuration --
+Llama-3-8B attention shape (32 query / 8 KV heads, head_dim 128), 64 concurrent sequences with
+seeded context lengths ~U[512, 8192], paged fp16 KV in 16-token blocks, one new token per
+sequence: KV append + split-KV attention + combine, for one attention layer.  The KV working set
+(~1.1 GB per GPU) is far larger than L2, so no L2 flush is needed between steps.
+
+  python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
+  python bench.py --impl reference ...                     (CPU oracle on the host cores)
+
+With N > 1 every rank owns its own 64 sequences (weak scaling, no collective on the data path);
+the timed region is bracketed by a barrier + synchronize and the maximum over ranks is reported.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "decode_attn_tok_per_s"
+UNIT = "tok/s"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"],
+                "tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons of one GPU while a region is timed."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def setup_decode(ctx, cfg, rank, device):
+    """Paged pools filled (through the append kernel) with seeded N(0,1) K/V for `cfg.batch`
+    sequences; returns everything a decode step needs."""
+    import torch
+
+    import hippo_leap_b200 as hl
+    from hippo_leap_b200 import synth
+
+    ctx_lens = synth.gen_ctx_lens(cfg, rank=rank)
+    tables, num_blocks = synth.gen_block_tables(ctx_lens, cfg.block_tokens, cfg.seed + rank)
+    shape = hl.AttnShape(cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
+    ctx.set_rope(cfg.theta())
+    kv = ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, cfg.block_tokens, num_blocks)
+    ttab = torch.from_numpy(tables).to(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1000 + cfg.seed + rank)
+    for i, c in enumerate(ctx_lens):
+        k = torch.randn((int(c), cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        v = torch.randn((int(c), cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        nb = (int(c) + cfg.block_tokens - 1) // cfg.block_tokens
+        ctx.kv_append_seq(kv, 0, shape, k, v, 0, ttab[i, :nb].contiguous())
+    B = len(ctx_lens)
+    q = torch.randn((B, cfg.n_head, cfg.head_dim), generator=gen, device=device)
+    kn = torch.randn((B, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+    vn = torch.randn((B, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+    out = torch.empty_like(q)
+    tctx = torch.from_numpy(ctx_lens).to(device)
+    ctx.sync()
+    return dict(shape=shape, kv=kv, ctx_lens=ctx_lens, tctx=tctx, ttab=ttab, q=q, kn=kn, vn=vn, out=out,
+                max_ctx=int(ctx_lens.max()))
+
+
+def cpu_decode_sample(cfg, n_seq, steps, n_threads):
+    """The CPU oracle on the first n_seq sequences of the same seeded workload: `steps` decode steps.
+    Returns seconds per step."""
+    import oracle
+    from hippo_leap_b200 import synth
+
+    ctx_lens = synth.gen_ctx_lens(cfg, rank=0)[:n_seq]
+    theta = cfg.theta()
+    g = np.random.Generator(np.random.PCG64(77))
+    caches = []
+    for c in ctx_lens:
+        sc = oracle.SeqCache(int(c), cfg.n_head_kv, cfg.head_dim)
+        sc.k[:] = g.standard_normal(sc.k.shape, dtype=np.float32)
+        sc.v[:] = g.standard_normal(sc.v.shape, dtype=np.float32)
+        caches.append(sc)
+    q = g.standard_normal((n_seq, 1, cfg.n_head, cfg.head_dim), dtype=np.float32)
+    k = g.standard_normal((n_seq, 1, cfg.n_head_kv, cfg.head_dim), dtype=np.float32)
+    v = g.standard_normal((n_seq, 1, cfg.n_head_kv, cfg.head_dim), dtype=np.float32)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        for i, sc in enumerate(caches):
+            sc.cur_len = int(ctx_lens[i]) - 1  # the step appends at ctx-1 and attends ctx keys
+            oracle.attn_forward(q[i], k[i], v[i], sc, theta=theta, rope_mode=oracle.ROPE_SPLIT_HALF,
+                                n_threads=n_threads)
+        times.append(time.perf_counter() - t0)
+    return times, ctx_lens
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the reference's float32 ops (the reference itself is
+    Nim and cannot be built here), all host threads, on a bounded sample of the same workload."""
+    if rank != 0:
+        return
+    import oracle
+    from hippo_leap_b200 import synth
+
+    cfg = synth.CONFIGS[4]
+    n_threads = oracle.max_threads()
+    n_seq = 16
+    times, ctx_lens = cpu_decode_sample(cfg, n_seq, args.warmup + args.steps, n_threads)
+    t = sum(times[args.warmup:])
+    value = n_seq * args.steps / t
+    sample = f"first {n_seq} of the 64 seeded sequences (ctx sum {int(ctx_lens.sum())}), one layer, {args.steps} steps"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": n_threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus):
+    return {"workload": "config 4: batched decode attention, Llama-3-8B shape, one layer",
+            "n_head": cfg.n_head, "n_head_kv": cfg.n_head_kv, "head_dim": cfg.head_dim,
+            "sequences_per_gpu": cfg.batch, "ctx_range": list(cfg.ctx_range), "kv": "paged fp16",
+            "block_tokens": cfg.block_tokens, "sharding": f"batch x{n_gpus} (own sequences per GPU, no collective)",
+            "l2": "KV working set ~1.1 GB per GPU >> 126 MB L2 (no flush needed)"}
+
+
+def timed_loop(torch, fn, steps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)  # ms
+
+
+def extras_single_gpu(ctx, torch, device, peaks, quick):
+    """Prefill TFLOP/s on the prefill configurations (one layer each), device-resident inputs."""
+    import hippo_leap_b200 as hl
+    from hippo_leap_b200 import synth
+
+    res = {}
+    for ci in (2, 3, 5):
+        cfg = synth.CONFIGS[ci]
+        S = cfg.prefill
+        gen = torch.Generator(device=device)
+        gen.manual_seed(2000 + ci)
+        qw = kw = None
+        if cfg.qk_norm:
+            qw = (torch.rand(cfg.head_dim, generator=gen, device=device) * 0.2 + 0.9)
+            kw = (torch.rand(cfg.head_dim, generator=gen, device=device) * 0.2 + 0.9)
+        shape = hl.AttnShape(cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF,
+                             cfg.rms_eps, qw, kw)
+        ctx.set_rope(cfg.theta())
+        bt = 128
+        nb = (S + bt - 1) // bt
+        kv = ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, nb)
+        table = torch.randperm(nb, generator=gen, device=device).to(torch.int32)
+        q = torch.randn((S, cfg.n_head, cfg.head_dim), generator=gen, device=device)
+        k = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        v = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        out = torch.empty((S, cfg.n_head, cfg.head_dim), dtype=torch.float16, device=device)
+        ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
+        n = 2 if quick else 5
+        for _ in range(2):
+            ctx.attn_prefill(kv, 0, shape, q, 0, table, out)
+        ms = timed_loop(torch, lambda: ctx.attn_prefill(kv, 0, shape, q, 0, table, out), n) / n
+        ms_app = timed_loop(torch, lambda: ctx.kv_append_seq(kv, 0, shape, k, v, 0, table), n) / n
+        fl = synth.prefill_flops(cfg.n_head, cfg.head_dim, S)
+        tf = fl / (ms * 1e-3) / 1e12
+        res[f"config{ci}_prefill"] = {
+            "workload": f"{cfg.name}: causal prefill of {S} tokens, one layer", "ms_attn": ms, "ms_kv_append": ms_app,
+            "tflops": tf, "frac_of_tensor_peak": tf / peaks["tflops"], "peak_tflops": peaks["tflops"],
+            "peak_src": peaks["src"], "flops": fl}
+        kv.destroy()
+        del q, k, v, out
+        torch.cuda.empty_cache()
+    return res
+
+
+def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
+    """Config 5 with KV heads split across ranks and one all-gather of the head outputs (fp16)."""
+    import hippo_leap_b200 as hl
+    from hippo_leap_b200 import synth
+
+    cfg = synth.CONFIGS[5]
+    S = cfg.prefill
+    hkv_l = cfg.n_head_kv // world
+    hq_l = cfg.n_head // world
+    gen = torch.Generator(device=device)
+    gen.manual_seed(3000 + rank)
+    shape = hl.AttnShape(hq_l, hkv_l, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
+    ctx.set_rope(cfg.theta())
+    bt = 128
+    nb = (S + bt - 1) // bt
+    kv = ctx.kv_create(1, hkv_l, cfg.head_dim, bt, nb)
+    table = torch.arange(nb, device=device, dtype=torch.int32)
+    q = torch.randn((S, hq_l, cfg.head_dim), generator=gen, device=device)
+    k = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
+    v = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
+    # head-major output so that rank-order concatenation is the final [n_head][S][hd] layout
+    out_l = torch.empty((hq_l, S, cfg.head_dim), dtype=torch.float16, device=device)
+    full = torch.empty((cfg.n_head, S, cfg.head_dim), dtype=torch.float16, device=device)
+    ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
+
+    def step():
+        ctx.attn_prefill(kv, 0, shape, q, 0, table, out_l.permute(1, 0, 2))
+        if world > 1:
+            dist.all_gather_into_tensor(full, out_l)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    n = 3
+    ms = timed_loop(torch, step, n) / n
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    fl = synth.prefill_flops(cfg.n_head, cfg.head_dim, S)
+    tf = fl / (ms * 1e-3) / 1e12
+    kv.destroy()
+    return {"workload": f"{cfg.name}: 32768-token causal prefill, KV heads {hkv_l}/GPU, fp16 all-gather of head outputs",
+            "ms": ms, "tflops_aggregate": tf, "frac_of_tensor_peak_per_gpu": tf / world / peaks["tflops"],
+            "scaling": "strong"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill side measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--decode-chunk", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import hippo_leap_b200 as hl
+    from hippo_leap_b200 import synth
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    peaks = load_peaks()
+    cfg = synth.CONFIGS[4]
+    ctx = hl.Context(local_rank, torch.cuda.current_stream())
+    ctx.set_tuning(args.decode_chunk, 0)
+    w = setup_decode(ctx, cfg, rank, device)
+    B = len(w["ctx_lens"])
+
+    def step():
+        ctx.kv_append_batch(w["kv"], 0, w["shape"], w["kn"], w["vn"], w["tctx"], w["ttab"])
+        ctx.attn_decode(w["kv"], 0, w["shape"], w["q"], w["tctx"], w["max_ctx"], w["ttab"], w["out"])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = ctx.launch_count()
+    ms_local = timed_loop(torch, step, args.steps)
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    t = torch.tensor([ms_local], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    value = world * B * args.steps / (ms_total * 1e-3)
+
+    # roofline of the dominant kernel pair (split-KV decode + combine), timed alone
+    for _ in range(3):
+        ctx.attn_decode(w["kv"], 0, w["shape"], w["q"], w["tctx"], w["max_ctx"], w["ttab"], w["out"])
+    ms_attn = timed_loop(torch, lambda: ctx.attn_decode(w["kv"], 0, w["shape"], w["q"], w["tctx"], w["max_ctx"],
+                                                        w["ttab"], w["out"]), args.steps) / args.steps
+    alg_bytes = synth.decode_bytes(w["ctx_lens"], cfg.n_head, cfg.n_head_kv, cfg.head_dim)
+    achieved = alg_bytes / (ms_attn * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel<128,...> + attn_combine_kernel<128>",
+                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "peak_src": peaks["src"], "traffic": None, "algorithmic_bytes_per_launch": alg_bytes,
+                "ms_per_launch": ms_attn}
+
+    # end to end through the host-buffer C ABI call: pinned host inputs, host result, every step
+    q_h, k_h, v_h = (x.cpu().pin_memory() for x in (w["q"], w["kn"], w["vn"]))
+    out_h = torch.empty_like(q_h).pin_memory()
+
+    def step_host():
+        ctx.decode_step_host(w["kv"], 0, w["shape"], q_h, k_h, v_h, w["tctx"], w["max_ctx"], w["ttab"], out_h)
+
+    for _ in range(3):
+        step_host()
+    if world > 1:
+        dist.barrier()
+    ms_e2e = timed_loop(torch, step_host, args.steps)
+    t2 = torch.tensor([ms_e2e], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_value = world * B * args.steps / (float(t2.item()) * 1e-3)
+    h2d = q_h.numel() * 4 + k_h.numel() * 4 + v_h.numel() * 4
+    d2h = out_h.numel() * 4
+    code, detail = ctx.device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code} (detail {detail}) after the timed region")
+
+    extra = {}
+    if not args.no_extras:
+        if world == 1:
+            extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False))
+        if cfg.n_head_kv % world == 0:
+            extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
+                                                                               peaks)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle
+        n_threads = oracle.max_threads()
+        n_seq = 16
+        times, cl = cpu_decode_sample(cfg, n_seq, 3, n_threads)
+        tt = sum(times[1:]) / 2
+        cpu_baseline = {"value": n_seq / tt, "unit": UNIT, "cores": n_threads, "kind": "port",
+                        "sample": f"first {n_seq} of the 64 seeded sequences (ctx sum {int(cl.sum())}), one layer, "
+                                  f"2 timed steps after 1 warm-up, {tt:.2f} s per step"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV, f32 accumulate", "data": "synthetic",
+            "config": workload_config(cfg, world),
+            "hbm_gbs": achieved, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": float(t2.item()) / args.steps},
+            "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    w["kv"].destroy()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,96 @@
+// Host-buffer forms of the two attention steps (declared in include/hl_b200.h).
+#include <cuda_runtime.h>
+
+#include "../../include/hl_b200.h"
+#include "host_common.h"
+
+namespace {
+
+int32_t ensure_stage(hl_ctx* ctx, int i, size_t bytes) {
+  if (bytes <= ctx->stage_cap[i]) return HL_OK;
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+  ctx->stage[i] = nullptr;
+  ctx->stage_cap[i] = 0;
+  HL_CUDA(ctx, cudaMalloc(&ctx->stage[i], bytes));
+  ctx->stage_cap[i] = bytes;
+  return HL_OK;
+}
+
+hl_view dense_view(void* p, int heads, int hd) {
+  return hl_view{p, HL_DTYPE_F32, static_cast<int64_t>(heads) * hd, hd, 1};
+}
+
+struct StepIo {
+  hl_view q, k, v, out;
+  size_t q_bytes, kv_bytes;
+};
+
+int32_t stage_in(hl_ctx* ctx, const hl_attn_shape* s, const float* q_h, const float* k_h, const float* v_h,
+                 int32_t n, float* out_h, StepIo* io) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!s || !q_h || !k_h || !v_h || !out_h) return hl_fail(ctx, HL_ERR_ARG, "host step: null argument");
+  if (n <= 0 || s->n_head <= 0 || s->n_head_kv <= 0 || s->head_dim <= 0)
+    return hl_fail(ctx, HL_ERR_ARG, "host step: non-positive size");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  io->q_bytes = static_cast<size_t>(n) * s->n_head * s->head_dim * sizeof(float);
+  io->kv_bytes = static_cast<size_t>(n) * s->n_head_kv * s->head_dim * sizeof(float);
+  int32_t rc = ensure_stage(ctx, 0, io->q_bytes);
+  if (rc == HL_OK) rc = ensure_stage(ctx, 1, io->kv_bytes);
+  if (rc == HL_OK) rc = ensure_stage(ctx, 2, io->kv_bytes);
+  if (rc == HL_OK) rc = ensure_stage(ctx, 3, io->q_bytes);
+  if (rc != HL_OK) return rc;
+  io->q = dense_view(ctx->stage[0], s->n_head, s->head_dim);
+  io->k = dense_view(ctx->stage[1], s->n_head_kv, s->head_dim);
+  io->v = dense_view(ctx->stage[2], s->n_head_kv, s->head_dim);
+  io->out = dense_view(ctx->stage[3], s->n_head, s->head_dim);
+  return HL_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t hl_b200_prefill_host(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                        const float* q_h, const float* k_h, const float* v_h, int32_t n_tok,
+                                        int32_t start_pos, const int32_t* block_table, int32_t n_blocks_in_table,
+                                        float* out_h, float* gpu_ms) {
+  StepIo io;
+  int32_t rc = stage_in(ctx, shape, q_h, k_h, v_h, n_tok, out_h, &io);
+  if (rc != HL_OK) return rc;
+  if (gpu_ms) HL_CUDA(ctx, cudaEventRecord(ctx->ev2, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.q.ptr, q_h, io.q_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.k.ptr, k_h, io.kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.v.ptr, v_h, io.kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  rc = hl_b200_kv_append_seq(ctx, kv, layer, shape, &io.k, &io.v, n_tok, start_pos, block_table, n_blocks_in_table);
+  if (rc == HL_OK)
+    rc = hl_b200_attn_prefill(ctx, kv, layer, shape, &io.q, n_tok, start_pos, block_table, n_blocks_in_table, &io.out,
+                              nullptr);
+  if (rc != HL_OK) return rc;
+  HL_CUDA(ctx, cudaMemcpyAsync(out_h, io.out.ptr, io.q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  if (gpu_ms) HL_CUDA(ctx, cudaEventRecord(ctx->ev3, ctx->stream));
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (gpu_ms) HL_CUDA(ctx, cudaEventElapsedTime(gpu_ms, ctx->ev2, ctx->ev3));
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_decode_step_host(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                            const float* q_h, const float* k_h, const float* v_h, int32_t batch,
+                                            const int32_t* ctx_lens, int32_t max_ctx_h, const int32_t* block_tables,
+                                            int32_t max_blocks_per_seq, float* out_h, float* gpu_ms) {
+  StepIo io;
+  int32_t rc = stage_in(ctx, shape, q_h, k_h, v_h, batch, out_h, &io);
+  if (rc != HL_OK) return rc;
+  if (gpu_ms) HL_CUDA(ctx, cudaEventRecord(ctx->ev2, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.q.ptr, q_h, io.q_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.k.ptr, k_h, io.kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  HL_CUDA(ctx, cudaMemcpyAsync(io.v.ptr, v_h, io.kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  rc = hl_b200_kv_append_batch(ctx, kv, layer, shape, &io.k, &io.v, batch, ctx_lens, block_tables, max_blocks_per_seq);
+  if (rc == HL_OK)
+    rc = hl_b200_attn_decode(ctx, kv, layer, shape, &io.q, batch, ctx_lens, max_ctx_h, block_tables,
+                             max_blocks_per_seq, &io.out, nullptr);
+  if (rc != HL_OK) return rc;
+  HL_CUDA(ctx, cudaMemcpyAsync(out_h, io.out.ptr, io.q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  if (gpu_ms) HL_CUDA(ctx, cudaEventRecord(ctx->ev3, ctx->stream));
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (gpu_ms) HL_CUDA(ctx, cudaEventElapsedTime(gpu_ms, ctx->ev2, ctx->ev3));
+  return HL_OK;
+}

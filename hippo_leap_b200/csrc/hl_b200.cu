@@ -36,14 +36,6 @@ int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...) {
   return code;
 }
 
-#define HL_CUDA(ctx, expr)                                                                   \
-  do {                                                                                       \
-    cudaError_t e_ = (expr);                                                                 \
-    if (e_ != cudaSuccess)                                                                   \
-      return hl_fail(ctx, HL_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
-                     __FILE__, __LINE__);                                                    \
-  } while (0)
-
 namespace {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -127,6 +119,7 @@ extern "C" int32_t hl_b200_create(int32_t device, void* stream, hl_ctx** out) {
     ctx->own_stream = true;
   }
   bool ok = cudaEventCreate(&ctx->ev0) == cudaSuccess && cudaEventCreate(&ctx->ev1) == cudaSuccess &&
+            cudaEventCreate(&ctx->ev2) == cudaSuccess && cudaEventCreate(&ctx->ev3) == cudaSuccess &&
             cudaMalloc(&ctx->status_d, 2 * sizeof(int32_t)) == cudaSuccess &&
             cudaMemset(ctx->status_d, 0, 2 * sizeof(int32_t)) == cudaSuccess;
   cudaDriverEntryPointQueryResult qres;
@@ -151,8 +144,12 @@ extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
   if (ctx->status_d) cudaFree(ctx->status_d);
   if (ctx->part_o) cudaFree(ctx->part_o);
   if (ctx->part_ml) cudaFree(ctx->part_ml);
+  for (void* p : ctx->stage)
+    if (p) cudaFree(p);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+  if (ctx->ev2) cudaEventDestroy(ctx->ev2);
+  if (ctx->ev3) cudaEventDestroy(ctx->ev3);
   if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return HL_OK;

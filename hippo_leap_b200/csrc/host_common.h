@@ -15,13 +15,15 @@ struct hl_ctx {
   int n_sm = 0;
   cudaStream_t stream = nullptr;
   bool own_stream = false;
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr, ev3 = nullptr;
   float* theta_d = nullptr;  // RoPE theta table [theta_half]
   int theta_half = 0;
   int32_t* status_d = nullptr;  // {code, detail} written by bounded waits / bounds checks
   float* part_o = nullptr;      // split-KV partial outputs (grow-only scratch)
   float* part_ml = nullptr;     // split-KV partial (max, sum)
   size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
+  void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // q, k, v, out staging of the *_host calls
+  size_t stage_cap[4] = {0, 0, 0, 0};
   void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved through the runtime
   int32_t decode_chunk = 0;
   int32_t prefill_kernel = 0;
@@ -38,3 +40,11 @@ struct hl_kv {
 };
 
 int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...);
+
+#define HL_CUDA(ctx, expr)                                                                   \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess)                                                                   \
+      return hl_fail(ctx, HL_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                     __FILE__, __LINE__);                                                    \
+  } while (0)

@@ -205,3 +205,31 @@ class Context:
             _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
             C.byref(oc), C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
+
+    # -- host-buffer forms (inputs and result in host memory; the call synchronises) ------------
+    @staticmethod
+    def _host_ptr(t: torch.Tensor):
+        assert (not t.is_cuda) and t.dtype == torch.float32 and t.is_contiguous()
+        return C.cast(t.data_ptr(), C.POINTER(C.c_float))
+
+    def prefill_host(self, kv: KvPool, layer: int, shape: AttnShape, q_h, k_h, v_h, start_pos: int,
+                     block_table: torch.Tensor, out_h: torch.Tensor, timed: bool = False):
+        sc = shape.c()
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_prefill_host(
+            self.handle, kv.handle, layer, C.byref(sc), self._host_ptr(q_h), self._host_ptr(k_h),
+            self._host_ptr(v_h), q_h.shape[0], start_pos, _i32_dev(block_table),
+            block_table.numel(), self._host_ptr(out_h), C.byref(ms) if timed else None))
+        return ms.value if timed else None
+
+    def decode_step_host(self, kv: KvPool, layer: int, shape: AttnShape, q_h, k_h, v_h,
+                         ctx_lens: torch.Tensor, max_ctx: int, block_tables: torch.Tensor,
+                         out_h: torch.Tensor, timed: bool = False):
+        sc = shape.c()
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_decode_step_host(
+            self.handle, kv.handle, layer, C.byref(sc), self._host_ptr(q_h), self._host_ptr(k_h),
+            self._host_ptr(v_h), q_h.shape[0], _i32_dev(ctx_lens), max_ctx,
+            _i32_dev(block_tables), block_tables.shape[1], self._host_ptr(out_h),
+            C.byref(ms) if timed else None))
+        return ms.value if timed else None

@@ -156,6 +156,23 @@ int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
                             int32_t max_ctx_h, const int32_t* block_tables,
                             int32_t max_blocks_per_seq, const hl_view* out, float* gpu_ms);
 
+/* ---- host-buffer forms ------------------------------------------------------------------
+ * The same two steps for callers whose activations live in HOST memory (float32, token-major
+ * contiguous: q [n][n_head][head_dim], k and v [n][n_head_kv][head_dim], out like q).  Each call
+ * copies its inputs to the device, runs append + attention, copies the result back and
+ * synchronises -- the shape of one reference forward call, which uploads its inputs and
+ * downloads its result around the kernels (naive.nim:4013, 4581-4584).  gpu_ms (optional)
+ * receives the device time of the whole step, copies included. */
+int32_t hl_b200_prefill_host(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                             const float* q_h, const float* k_h, const float* v_h, int32_t n_tok,
+                             int32_t start_pos, const int32_t* block_table,
+                             int32_t n_blocks_in_table, float* out_h, float* gpu_ms);
+int32_t hl_b200_decode_step_host(hl_ctx* ctx, hl_kv* kv, int32_t layer,
+                                 const hl_attn_shape* shape, const float* q_h, const float* k_h,
+                                 const float* v_h, int32_t batch, const int32_t* ctx_lens,
+                                 int32_t max_ctx_h, const int32_t* block_tables,
+                                 int32_t max_blocks_per_seq, float* out_h, float* gpu_ms);
+
 /* Tunables (0 = automatic): tokens per split-KV chunk for decode; which prefill kernel
  * runs (0 auto, 1 = warp-MMA kernel, 2 = tcgen05 kernel). */
 int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, int32_t prefill_kernel);
