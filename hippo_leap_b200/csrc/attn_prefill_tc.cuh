@@ -1,10 +1,571 @@
-// tcgen05 / TMEM causal GQA prefill (placeholder while the warp-MMA kernel is brought up).
+// Causal GQA prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators,
+// TMA-staged K/V, fp32 online softmax with one thread per query row.
+// Replaces qkNormPrefill(Q) + ropeAtPos(Q) + attentionPrefillKernel of the reference
+// (src/hippo_leap/backends/naive.nim:2928-2971, 3006-3044, 3385-3464).
+//
+// One CTA = 256 query rows of one head, as two 128-row tiles A and B that ping-pong on the tensor
+// core: while the softmax warps of one tile work on S = Q K^T, the MMA warp runs the other tile.
+//   warps 0-3  softmax of tile A  (thread r owns row r: TMEM lane r, no shuffles in the softmax)
+//   warps 4-7  softmax of tile B
+//   warp  8    TMA producer: K and V blocks of 128 keys from the paged cache, 128-byte swizzle
+//   warp  9    MMA issuer (one elected lane) and TMEM owner
+// TMEM (512 columns): S_A, S_B (128 fp32 columns each; P, as fp16 pairs, overwrites the first 64
+// columns of its S once the row has been read), O_A, O_B (head_dim columns each).
+//   S_t  = Q_t K_j^T    tcgen05.mma kind::f16, A and B from shared memory (K-major, SW128)
+//   O_t += P_t V_j      A from TMEM, B = V from shared memory as an MN-major SW128 operand
+// The running maximum is only raised when it grows by more than 2^8 (the O rescale in TMEM then
+// happens rarely); the final division by the row sum restores exactness.
+// The query prologue (RMSNorm, RoPE from a cos/sin table built with full-precision sincosf, fp16)
+// is done by the softmax warps while the first K/V blocks are in flight.
+// Every wait is bounded; a timeout raises the status word, makes all later waits of the CTA fall
+// through, and TMEM is always released before the CTA exits.
 #pragma once
+#include <cuda.h>
+
 #include "attn_prefill_mma.cuh"
+#include "hl_device.cuh"
 #include "host_common.h"
 
-inline bool hl_prefill_tc_supported(const hl::PrefillArgs&, int) { return false; }
-inline bool hl_prefill_tc_default(const hl::PrefillArgs&, int) { return false; }
-inline int32_t hl_launch_prefill_tc(hl_ctx* ctx, hl_kv*, int32_t, const hl::PrefillArgs&, int) {
-  return hl_fail(ctx, HL_ERR_UNSUPPORTED, "tcgen05 prefill kernel not built");
+namespace hl {
+
+struct PrefillTcArgs {
+  PrefillArgs p;
+  const float2* cs_table;  // [n_pos][rope_dim/2] (cos, sin) of float(pos) * theta_i
+  int32_t box_rows;        // rows per TMA box: 16, or 128 when a block holds whole 128-key tiles
+  uint32_t oob_row;        // a row coordinate outside the pool: TMA fills such boxes with zeros
+};
+
+// ---- tcgen05 wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+#define HL_R32(a, o)                                                                                        \
+  a[o + 0], a[o + 1], a[o + 2], a[o + 3], a[o + 4], a[o + 5], a[o + 6], a[o + 7], a[o + 8], a[o + 9],        \
+      a[o + 10], a[o + 11], a[o + 12], a[o + 13], a[o + 14], a[o + 15], a[o + 16], a[o + 17], a[o + 18],    \
+      a[o + 19], a[o + 20], a[o + 21], a[o + 22], a[o + 23], a[o + 24], a[o + 25], a[o + 26], a[o + 27],    \
+      a[o + 28], a[o + 29], a[o + 30], a[o + 31]
+// 32 consecutive TMEM columns of this thread's lane -> 32 registers
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32f(uint32_t taddr, float* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+        "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+        "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+        "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32f(uint32_t taddr, const float* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31,%32};" ::"r"(taddr),
+      "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]),
+      "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]), "f"(r[16]), "f"(r[17]), "f"(r[18]),
+      "f"(r[19]), "f"(r[20]), "f"(r[21]), "f"(r[22]), "f"(r[23]), "f"(r[24]), "f"(r[25]), "f"(r[26]), "f"(r[27]),
+      "f"(r[28]), "f"(r[29]), "f"(r[30]), "f"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Shared-memory matrix descriptors (sm_100 format): start address, leading / stride byte offsets in
+// 16-byte units, version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: fp16 A and B, fp32 accumulator, M x N, B major selectable.
+__host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+template <int HD>
+struct PrefillTcCfg {
+  static constexpr int kStages = HD == 128 ? 2 : 4;
+  static constexpr int kHalves = HD / 64;
+  static constexpr int kHalfBytes = 128 * 128;              // 128 rows x 64 halfs
+  static constexpr int kTileBytes = kHalves * kHalfBytes;   // one Q tile, one K block or one V block
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = 2 * kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kTileBytes;
+  static constexpr int kRowOff = kVOff + kStages * kTileBytes;  // fp32 row staging, 8 warps (slow prologue)
+  static constexpr int kBarOff = kRowOff + 8 * HD * 4;
+  static constexpr int kNumBars = 4 * kStages + 7;
+  static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 16;
+  static constexpr int kThreads = 320;
+  static constexpr int kTmemCols = 512;
+  static constexpr uint32_t kColS = 0, kColO = 256;  // S_t at t*128, O_t at 256 + t*HD
+};
+
+// Bounded wait that also gives up at once when the CTA has already seen a timeout.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, int32_t* status, int32_t where,
+                                        volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  report(status, HL_ERR_TIMEOUT, where);
+  return false;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(320, 1)
+    attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                           PrefillTcArgs ta) {
+  using Cfg = PrefillTcCfg<HD>;
+  constexpr int S = Cfg::kStages;
+  const PrefillArgs& a = ta.p;
+  const int q_blk = gridDim.x - 1 - blockIdx.x;  // longest first
+  const int h = blockIdx.y;
+  const int kvh = h / a.group;
+  const int t0 = q_blk * 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + Cfg::kBarOff);
+  uint64_t* k_full = bars;
+  uint64_t* k_empty = bars + S;
+  uint64_t* v_full = bars + 2 * S;
+  uint64_t* v_empty = bars + 3 * S;
+  uint64_t* s_full = bars + 4 * S;      // [2]
+  uint64_t* p_full = bars + 4 * S + 2;  // [2]
+  uint64_t* o_full = bars + 4 * S + 4;  // [2]
+  uint64_t* q_ready = bars + 4 * S + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // keys attended by tile t: [0, k_end[t]); 128-key blocks: n_blk[t]
+  int k_end[2], n_blk[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int live = min(128, a.n_tok - (t0 + 128 * t));
+    k_end[t] = live > 0 ? a.start_pos + t0 + 128 * t + live : 0;
+    n_blk[t] = (k_end[t] + 127) >> 7;
+  }
+  const int n_max = max(n_blk[0], n_blk[1]);
+  const int k_end_max = max(k_end[0], k_end[1]);
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&o_full[t], 1);
+    }
+    mbar_init(q_ready, 256);
+    *abort_flag = (a.status != nullptr && *a.status != 0) ? 1 : 0;  // an earlier CTA already failed
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      tma_prefetch_desc(&k_map);
+      tma_prefetch_desc(&v_map);
+    }
+    const int boxes_per_half = 128 / ta.box_rows;           // 8 or 1
+    const int n_boxes = boxes_per_half * Cfg::kHalves;      // per K (or V) block: <= 16
+    const int box_bytes = ta.box_rows * 128;
+    for (int j = 0; j < n_max; ++j) {
+      const int s = j % S;
+      const uint32_t par = ((j / S) - 1) & 1;
+      // this lane's box of the block: which row group, which column half
+      const int grp = lane / Cfg::kHalves, hh = lane % Cfg::kHalves;
+      int row = static_cast<int>(ta.oob_row);
+      if (lane < n_boxes) {
+        const int tok = j * 128 + grp * ta.box_rows;
+        if (tok < k_end_max) {
+          const int lb = tok / a.block_tokens;
+          int pb = lb < a.n_blocks_in_table ? a.block_table[lb] : -1;
+          if (pb < 0 || pb >= a.num_blocks) {
+            report(a.status, HL_ERR_BOUNDS, lb);
+            pb = 0;
+          }
+          row = (pb * a.n_head_kv + kvh) * a.block_tokens + tok % a.block_tokens;
+        }
+      }
+      const uint32_t dst_off = hh * Cfg::kHalfBytes + grp * box_bytes;
+      // K block j
+      if (j >= S) tc_wait(&k_empty[s], par, a.status, 500 + s, abort_flag);
+      if (lane == 0) mbar_arrive_expect_tx(&k_full[s], Cfg::kTileBytes);
+      __syncwarp();
+      if (lane < n_boxes)
+        tma_load_2d(base + Cfg::kKOff + s * Cfg::kTileBytes + dst_off, &k_map, &k_full[s], hh * 64, row);
+      // V block j
+      if (j >= S) tc_wait(&v_empty[s], par, a.status, 510 + s, abort_flag);
+      if (lane == 0) mbar_arrive_expect_tx(&v_full[s], Cfg::kTileBytes);
+      __syncwarp();
+      if (lane < n_boxes)
+        tma_load_2d(base + Cfg::kVOff + s * Cfg::kTileBytes + dst_off, &v_map, &v_full[s], hh * 64, row);
+      __syncwarp();
+    }
+  } else if (warp == 9) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(128, 128, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
+      auto issue_qk = [&](int t, int j) {
+        const uint32_t a_base = base + Cfg::kQOff + t * Cfg::kTileBytes;
+        const uint32_t b_base = base + Cfg::kKOff + (j % S) * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * Cfg::kHalfBytes + (ks & 3) * 32;
+          tc_mma_ss(tmem + Cfg::kColS + t * 128, umma_desc(a_base + off, 16, 1024), umma_desc(b_base + off, 16, 1024),
+                    idesc_qk, ks > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t b_base = base + Cfg::kVOff + (j % S) * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          tc_mma_ts(tmem + Cfg::kColO + t * HD, tmem + Cfg::kColS + t * 128 + ks * 8,
+                    umma_desc(b_base + ks * 2048, Cfg::kHalfBytes, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+      };
+      tc_wait(q_ready, 0, a.status, 520, abort_flag);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_after();
+      if (n_max > 0) {
+        tc_wait(&k_full[0], 0, a.status, 521, abort_flag);
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (n_blk[t] > 0) {
+            issue_qk(t, 0);
+            tc_commit(&s_full[t]);
+          }
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_max; ++j) {
+        bool next_qk = false;
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_blk[t]) continue;
+          tc_wait(&p_full[t], j & 1, a.status, 530 + t, abort_flag);
+          tc_wait(&v_full[j % S], (j / S) & 1, a.status, 532, abort_flag);
+          tc_fence_after();
+          issue_pv(t, j);
+          if (j + 1 < n_blk[t]) {
+            tc_wait(&k_full[(j + 1) % S], ((j + 1) / S) & 1, a.status, 533, abort_flag);
+            tc_fence_after();
+            issue_qk(t, j + 1);
+            tc_commit(&s_full[t]);
+            next_qk = true;
+          } else {
+            tc_commit(&o_full[t]);
+          }
+        }
+        tc_commit(&v_empty[j % S]);
+        if (next_qk) tc_commit(&k_empty[(j + 1) % S]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ======================= softmax warps (tile t, row r) =======================
+    const int t = warp >> 2;
+    const int r = tid & 127;
+    const int trow = t0 + 128 * t + r;          // token index of this thread's row
+    const int pos = a.start_pos + trow;         // its position
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_sel + Cfg::kColS + t * 128;
+    const uint32_t tO = tmem + lane_sel + Cfg::kColO + t * HD;
+
+    // ---- Q prologue: this warp prepares rows [32*(warp&3), +32) of tile t ----
+    {
+      const uint32_t q_tile = base + Cfg::kQOff + t * Cfg::kTileBytes;
+      constexpr int VEC = HD / 32;
+      const bool fast = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
+      float* xrow = reinterpret_cast<float*>(gen + Cfg::kRowOff) + warp * HD;
+      for (int rr = 0; rr < 32; ++rr) {
+        const int row = (warp & 3) * 32 + rr;
+        const int tt = t0 + 128 * t + row;
+        const bool live = tt < a.n_tok;
+        if (fast) {
+          float x[VEC];
+          const int d0 = lane * VEC;
+          if (live) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) x[e] = view_load(a.q, tt, h, d0 + e);
+            if (a.q_norm_w != nullptr) {
+              float ss = 0.f;
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) ss += x[e] * x[e];
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+              const float inv = 1.0f / sqrtf(ss / static_cast<float>(HD) + a.eps);
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) x[e] = x[e] * inv * a.q_norm_w[d0 + e];
+            }
+            const float2* cs = ta.cs_table + static_cast<int64_t>(a.start_pos + tt) * (HD / 2);
+            if (a.rope_mode == HL_ROPE_INTERLEAVED) {
+#pragma unroll
+              for (int e = 0; e < VEC; e += 2) {
+                const float2 c = cs[(d0 + e) >> 1];
+                const float v0 = x[e], v1 = x[e + 1];
+                x[e] = v0 * c.x - v1 * c.y;
+                x[e + 1] = v0 * c.y + v1 * c.x;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+                const int d = d0 + e;
+                if (d < HD / 2) {
+                  const float2 c = cs[d];
+                  x[e] = x[e] * c.x - other * c.y;
+                } else {
+                  const float2 c = cs[d - HD / 2];
+                  x[e] = other * c.y + x[e] * c.x;
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+          }
+          const uint32_t addr = swz128(q_tile + (d0 >> 6) * Cfg::kHalfBytes, row, (d0 & 63) >> 3) + (d0 & 7) * 2;
+          if constexpr (VEC == 4) {
+            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(pack_half2(x[0], x[1])),
+                         "r"(pack_half2(x[2], x[3]))
+                         : "memory");
+          } else {
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack_half2(x[0], x[1])) : "memory");
+          }
+        } else {
+          if (live) {
+#pragma unroll
+            for (int d = lane; d < HD; d += 32) xrow[d] = view_load(a.q, tt, h, d);
+            __syncwarp();
+            norm_rope_row<HD>(xrow, a.q_norm_w, a.eps, a.theta, a.rope_dim, a.rope_mode, a.start_pos + tt, lane);
+          }
+          store_row_fp16_swz<HD>(q_tile, Cfg::kHalfBytes, row, xrow, lane, !live);
+          __syncwarp();
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(q_ready);
+    }
+
+    float m = -INFINITY, l = 0.f;
+    const float c = a.scale_log2;
+    for (int j = 0; j < n_blk[t]; ++j) {
+      float s[128];
+      tc_wait(&s_full[t], j & 1, a.status, 540 + t, abort_flag);
+      tc_fence_after();
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tc_ld32f(tS + q4 * 32, s + q4 * 32);
+      tc_wait_ld();
+      const int key0 = j * 128;
+      if (key0 + 127 > a.start_pos + t0 + 128 * t) {  // block touches this tile's diagonal
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (key0 + i > pos) s[i] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      if (j == 0) {
+        m = mx;
+      } else {
+        const bool need = (mx - m) * c > 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float f = need ? fast_exp2((m - mx) * c) : 1.0f;
+          if (need) m = mx;
+          l *= f;
+#pragma unroll
+          for (int q4 = 0; q4 < HD / 32; ++q4) {
+            float oreg[32];
+            tc_ld32f(tO + q4 * 32, oreg);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] *= f;
+            tc_st32f(tO + q4 * 32, oreg);
+          }
+          tc_wait_st();
+        }
+      }
+      const float mc = m * c;
+      float sum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        const float p0 = fast_exp2(fmaf(s[i], c, -mc));
+        const float p1 = fast_exp2(fmaf(s[i + 1], c, -mc));
+        sum += p0 + p1;
+        pk[i >> 1] = pack_half2(p0, p1);
+      }
+      l += sum;
+      tc_st32(tS, pk);
+      tc_st32(tS + 32, pk + 32);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+    // ---- epilogue: O / l -> out ----
+    if (n_blk[t] > 0) {
+      tc_wait(&o_full[t], 0, a.status, 550 + t, abort_flag);
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool live = trow < a.n_tok;
+#pragma unroll
+      for (int q4 = 0; q4 < HD / 32; ++q4) {
+        float oreg[32];
+        tc_ld32f(tO + q4 * 32, oreg);
+        tc_wait_ld();
+        if (live) {
+          if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
+            __half* dst = static_cast<__half*>(const_cast<void*>(a.out.ptr)) + static_cast<int64_t>(trow) * a.out.ts +
+                          static_cast<int64_t>(h) * a.out.hs + q4 * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              *reinterpret_cast<uint32_t*>(dst + i) =
+                  pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) view_store(a.out, trow, h, q4 * 32 + i, oreg[i] * inv);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everything issued has completed (or timed out); release TMEM ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::kTmemCols) : "memory");
+  }
+}
+
+// cos/sin table for the query prologue: out[p][i] = (cos, sin)(float(p) * theta[i]), full-precision sincosf.
+__global__ void rope_table_kernel(const float* __restrict__ theta, int half, int n_pos, float2* __restrict__ out) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(n_pos) * half) return;
+  const int p = static_cast<int>(idx / half), i = static_cast<int>(idx % half);
+  float s, c;
+  sincosf(static_cast<float>(p) * theta[i], &s, &c);
+  out[idx] = make_float2(c, s);
+}
+
+}  // namespace hl
+
+// The tcgen05 kernel takes every shape the warp-MMA kernel takes except tiny problems, where launching
+// 256-row CTAs wastes most of the tile.
+inline bool hl_prefill_tc_supported(const hl::PrefillArgs& a, int head_dim) {
+  return (head_dim == 64 || head_dim == 128) && a.n_tok >= 1;
+}
+inline bool hl_prefill_tc_default(const hl::PrefillArgs& a, int head_dim) {
+  return hl_prefill_tc_supported(a, head_dim) && a.n_tok >= 256;
+}
+
+template <int HD>
+static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a) {
+  using namespace hl;
+  using Cfg = PrefillTcCfg<HD>;
+  auto kern = attn_prefill_tc_kernel<HD>;
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[ctx->device & 15] = true;
+  }
+  // cos/sin table up to the last position of this call (grow-only, rebuilt when theta changes)
+  const int n_pos = a.start_pos + a.n_tok;
+  const int half = a.rope_dim / 2;
+  PrefillTcArgs ta{};
+  ta.p = a;
+  ta.cs_table = nullptr;
+  if (a.rope_dim == HD) {
+    if (ctx->cs_len < n_pos || ctx->cs_half != half) {
+      HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      if (ctx->cs_table) cudaFree(ctx->cs_table);
+      ctx->cs_table = nullptr;
+      ctx->cs_len = 0;
+      const int cap = ((n_pos + 4095) / 4096) * 4096;
+      HL_CUDA(ctx, cudaMalloc(&ctx->cs_table, static_cast<size_t>(cap) * half * sizeof(float2)));
+      const int64_t total = static_cast<int64_t>(cap) * half;
+      rope_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, ctx->stream>>>(
+          ctx->theta_d, half, cap, static_cast<float2*>(ctx->cs_table));
+      ctx->launches++;
+      HL_CUDA(ctx, cudaGetLastError());
+      ctx->cs_len = cap;
+      ctx->cs_half = half;
+    }
+    ta.cs_table = static_cast<const float2*>(ctx->cs_table);
+  }
+  const bool wide = kv->block_tokens % 128 == 0;
+  ta.box_rows = wide ? 128 : 16;
+  ta.oob_row = static_cast<uint32_t>(static_cast<uint64_t>(kv->num_blocks) * kv->n_head_kv * kv->block_tokens);
+  dim3 grid((a.n_tok + 255) / 256, a.n_head);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(wide ? kv->k_map128[layer] : kv->k_map[layer],
+                                                              wide ? kv->v_map128[layer] : kv->v_map[layer], ta);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
+inline int32_t hl_launch_prefill_tc(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a, int head_dim) {
+  return head_dim == 64 ? hl_launch_prefill_tc_t<64>(ctx, kv, layer, a) : hl_launch_prefill_tc_t<128>(ctx, kv, layer, a);
 }

@@ -146,6 +146,7 @@ extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
   if (ctx->part_ml) cudaFree(ctx->part_ml);
   for (void* p : ctx->stage)
     if (p) cudaFree(p);
+  if (ctx->cs_table) cudaFree(ctx->cs_table);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->ev2) cudaEventDestroy(ctx->ev2);
@@ -247,6 +248,7 @@ extern "C" int32_t hl_b200_set_rope(hl_ctx* ctx, const float* theta_h, int32_t h
     HL_CUDA(ctx, cudaMalloc(&ctx->theta_d, half * sizeof(float)));
   }
   ctx->theta_half = half;
+  ctx->cs_len = 0;  // the cos/sin table of the tcgen05 prefill is rebuilt from the new theta
   HL_CUDA(ctx, cudaMemcpy(ctx->theta_d, theta_h, half * sizeof(float), cudaMemcpyHostToDevice));
   return HL_OK;
 }

@@ -24,6 +24,8 @@ struct hl_ctx {
   size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // q, k, v, out staging of the *_host calls
   size_t stage_cap[4] = {0, 0, 0, 0};
+  void* cs_table = nullptr;  // float2 [cs_len][cs_half]: (cos, sin) of float(pos) * theta_i
+  int cs_len = 0, cs_half = 0;
   void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved through the runtime
   int32_t decode_chunk = 0;
   int32_t prefill_kernel = 0;
