@@ -35,18 +35,22 @@ def _setup(hl_ctx, n_head, n_head_kv, hd, S_total, bt, rope_mode, norm, seed, ba
     (64, 4, 1, 17, 32, hl.HL_ROPE_INTERLEAVED, True),
     (128, 8, 1, 257, 64, hl.HL_ROPE_SPLIT_HALF, False),
     (128, 4, 2, 513, 128, hl.HL_ROPE_INTERLEAVED, False),
+    (128, 4, 2, 640, 128, hl.HL_ROPE_SPLIT_HALF, True),
+    (64, 8, 2, 300, 16, hl.HL_ROPE_SPLIT_HALF, False),
 ])
-def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm):
+@pytest.mark.parametrize("kernel", [1, 2], ids=["mma", "tcgen05"])
+def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm, kernel):
     g, theta, qw, kw, shape, kv, table = _setup(hl_ctx, n_head, n_head_kv, hd, S, bt, rope_mode, norm, 11)
     q = g.standard_normal((S, n_head, hd), dtype=np.float32)
     k = g.standard_normal((S, n_head_kv, hd), dtype=np.float32)
     v = g.standard_normal((S, n_head_kv, hd), dtype=np.float32)
     tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
     tt = torch.from_numpy(table).cuda()
-    hl_ctx.set_tuning(0, 1)
+    hl_ctx.set_tuning(0, kernel)
     hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
     out = hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt)
     got = out.cpu().numpy()
+    hl_ctx.set_tuning(0, 0)
     want = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw)
     want16 = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw, kv_fp16=True)
     assert_parity(got, want, "prefill vs fp32 oracle")
@@ -92,11 +96,11 @@ def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs,
                                 q_norm_w=qw, k_norm_w=kw, kv_fp16=fp16,
                                 prefix=(kp, vp) if c > 1 else None)[0]
     tctx = torch.from_numpy(ctxs).cuda()
-    hl_ctx.set_tuning(chunk, 1)
+    hl_ctx.set_tuning(chunk, 0)
     hl_ctx.kv_append_batch(kv, 0, shape, torch.from_numpy(kn).cuda(), torch.from_numpy(vn).cuda(), tctx, ttab)
     out = hl_ctx.attn_decode(kv, 0, shape, torch.from_numpy(qn).cuda(), tctx, int(ctxs.max()), ttab)
     got = out.cpu().numpy()
-    hl_ctx.set_tuning(0, 1)
+    hl_ctx.set_tuning(0, 0)
     assert_parity(got, want, "decode vs fp32 oracle")
     assert_parity(got, want16, "decode vs fp16-KV oracle", 1e-3, 6e-4)
     kv.destroy()
