@@ -1,0 +1,382 @@
+// The reference's backend contract over the B200 attention path (C ABI in include/hl_backend.h),
+// with an attention-only stand-in model around it.  The orchestration mirrors the order of
+// operations of forwardPrefill / forwardDecode (src/hippo_leap/backends/naive.nim:4063-4078,
+// 4697-4717): per layer  Q/K/V rows -> [QK-norm -> RoPE -> KV store -> attention]  -> logits.
+// The bracketed part is the product path (libhl_b200 entry points); the row lookup and the logits
+// product around it are plain glue kernels.
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hl_backend.h"
+#include "host_common.h"
+
+namespace {
+
+struct Backend {
+  hl_ctx* ctx = nullptr;
+  int device = -1;
+  bool loaded = false;
+  hl_hparams hp{};
+  float *eq = nullptr, *ek = nullptr, *ev = nullptr, *wout = nullptr, *qn = nullptr, *kn = nullptr;
+  float *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr;  // activations [cap][dim]
+  int act_cap = 0;
+  float* logits_d = nullptr;
+  int32_t* tokens_d = nullptr;
+  int tokens_cap = 0;
+  int32_t* ctx_len_d = nullptr;  // one-sequence ctx_lens for the decode step
+  int32_t* table_d = nullptr;    // identity block table of the single sequence
+  int table_len = 0;
+  int32_t* next_d = nullptr;
+  int32_t* status_h = nullptr;  // pinned copy of the device status word
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  std::string err;
+} g;
+
+int32_t bfail(int32_t code, const char* msg) {
+  g.err = msg;
+  return code;
+}
+int32_t bfail_ctx(int32_t code, const char* call) {
+  const char* inner = g.ctx ? hl_b200_last_error(g.ctx) : "";
+  g.err = (inner && *inner) ? std::string(inner) : std::string(call) + " failed";
+  return code;
+}
+#define B_CUDA(expr)                                                    \
+  do {                                                                  \
+    cudaError_t e_ = (expr);                                            \
+    if (e_ != cudaSuccess) return bfail(HL_ERR_CUDA, cudaGetErrorString(e_)); \
+  } while (0)
+// B_TRY wraps a libhl_b200 call (its message comes from the context); B_PASS forwards the status of a
+// backend helper that has already recorded its own message.
+#define B_TRY(expr)                          \
+  do {                                       \
+    int32_t rc_ = (expr);                    \
+    if (rc_ != HL_OK) return bfail_ctx(rc_, #expr); \
+  } while (0)
+#define B_PASS(expr)              \
+  do {                            \
+    int32_t rc_ = (expr);         \
+    if (rc_ != HL_OK) return rc_; \
+  } while (0)
+
+int32_t ensure_ctx(int device) {
+  if (g.ctx) return device == g.device ? HL_OK : bfail(HL_ERR_ARG, "backend already bound to another device");
+  int32_t rc = hl_b200_create(device, nullptr, &g.ctx);
+  if (rc != HL_OK) return bfail(rc, "hl_b200_create failed: no usable sm_100 device (no CPU fallback exists)");
+  g.device = device;
+  return HL_OK;
+}
+
+// rows of the per-layer tables selected by the token ids: dst[t][:] = table[token[t]][:]
+__global__ void gather_rows_kernel(const float* __restrict__ table, const int32_t* __restrict__ tokens, int dim,
+                                   int n_vocab, float* __restrict__ dst) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
+  const float4* src = reinterpret_cast<const float4*>(table + static_cast<int64_t>(tok) * dim);
+  float4* d = reinterpret_cast<float4*>(dst + static_cast<int64_t>(t) * dim);
+  for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) d[i] = src[i];
+}
+
+// x = sum over layers of the last token's attention output (layer order, float32 adds);
+// logits[v] = sum_d x[d] * wout[d][v], d ascending, separate multiply and add (no FMA contraction),
+// i.e. the k-innermost float32 accumulation of the reference's CPU matmul (tensor.nim:77-80).
+__global__ void logits_kernel(const float* __restrict__ outs, int n_layer, int64_t layer_stride, int q_dim,
+                              const float* __restrict__ wout, int n_vocab, float* __restrict__ logits) {
+  extern __shared__ float x[];
+  for (int d = threadIdx.x; d < q_dim; d += blockDim.x) {
+    float acc = outs[d];
+    for (int l = 1; l < n_layer; ++l) acc = __fadd_rn(acc, outs[l * layer_stride + d]);
+    x[d] = acc;
+  }
+  __syncthreads();
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= n_vocab) return;
+  float acc = 0.f;
+  for (int d = 0; d < q_dim; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d], wout[static_cast<int64_t>(d) * n_vocab + v]));
+  logits[v] = acc;
+}
+
+// first maximal index wins, as argmaxLast (src/hippo_leap/sampling.nim:13-19)
+__global__ void argmax_first_kernel(const float* __restrict__ logits, int n, int32_t* __restrict__ out) {
+  __shared__ float bv[256];
+  __shared__ int bi[256];
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best || (v == best && i < idx)) {
+      best = v;
+      idx = i;
+    }
+  }
+  bv[threadIdx.x] = best;
+  bi[threadIdx.x] = idx;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = bv[threadIdx.x + s];
+      const int oi = bi[threadIdx.x + s];
+      if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
+        bv[threadIdx.x] = ov;
+        bi[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = bi[0];
+}
+
+__global__ void set_i32_kernel(int32_t* p, int32_t v) { *p = v; }
+
+int32_t check_hp(const hl_hparams* hp) {
+  if (!hp) return bfail(HL_ERR_ARG, "null hparams");
+  if (hp->n_head <= 0 && hp->n_layer > 0) return bfail(HL_ERR_ARG, "model requires head_count or SSM parameters");
+  if (hp->n_vocab <= 0 || hp->n_layer <= 0 || hp->n_head_kv <= 0) return bfail(HL_ERR_ARG, "non-positive hparam");
+  if (hp->n_head % hp->n_head_kv != 0) return bfail(HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
+  if (hp->head_dim != 64 && hp->head_dim != 128) return bfail(HL_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+  return HL_OK;
+}
+
+int32_t ensure_act(int n_tok) {
+  if (n_tok <= g.act_cap) return HL_OK;
+  cudaStreamSynchronize(g.ctx->stream);
+  for (float** p : {&g.q, &g.k, &g.v, &g.out}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  g.act_cap = 0;
+  const size_t qd = static_cast<size_t>(g.hp.n_head) * g.hp.head_dim, kd = static_cast<size_t>(g.hp.n_head_kv) * g.hp.head_dim;
+  B_CUDA(cudaMalloc(&g.q, n_tok * qd * sizeof(float)));
+  B_CUDA(cudaMalloc(&g.k, n_tok * kd * sizeof(float)));
+  B_CUDA(cudaMalloc(&g.v, n_tok * kd * sizeof(float)));
+  B_CUDA(cudaMalloc(&g.out, static_cast<size_t>(g.hp.n_layer) * n_tok * qd * sizeof(float)));
+  g.act_cap = n_tok;
+  return HL_OK;
+}
+
+hl_attn_shape shape_for_layer(int l) {
+  hl_attn_shape s{};
+  s.n_head = g.hp.n_head;
+  s.n_head_kv = g.hp.n_head_kv;
+  s.head_dim = g.hp.head_dim;
+  s.rope_dim = g.hp.rope_dim > 0 ? g.hp.rope_dim : g.hp.head_dim;  // naive.nim:3979
+  s.rope_mode = g.hp.rope_mode;
+  s.rms_eps = g.hp.rms_eps;
+  s.q_norm_w = g.qn ? g.qn + static_cast<size_t>(l) * g.hp.head_dim : nullptr;
+  s.k_norm_w = g.kn ? g.kn + static_cast<size_t>(l) * g.hp.head_dim : nullptr;
+  return s;
+}
+
+// One forward over n tokens starting at position pos0; decode is n == 1.
+int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode) {
+  hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
+  const int qd = g.hp.n_head * g.hp.head_dim, kd = g.hp.n_head_kv * g.hp.head_dim;
+  B_CUDA(cudaSetDevice(g.device));
+  if (ensure_act(n) != HL_OK) return HL_ERR_CUDA;
+  if (n > g.tokens_cap) {
+    cudaStreamSynchronize(g.ctx->stream);
+    if (g.tokens_d) cudaFree(g.tokens_d);
+    g.tokens_d = nullptr;
+    B_CUDA(cudaMalloc(&g.tokens_d, n * sizeof(int32_t)));
+    g.tokens_cap = n;
+  }
+  cudaStream_t st = g.ctx->stream;
+  B_CUDA(cudaMemcpyAsync(g.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  if (decode) set_i32_kernel<<<1, 1, 0, st>>>(g.ctx_len_d, pos0 + 1);
+  const int64_t layer_stride = static_cast<int64_t>(g.act_cap) * qd;
+  for (int l = 0; l < g.hp.n_layer; ++l) {
+    const size_t toff = static_cast<size_t>(l) * g.hp.n_vocab;
+    gather_rows_kernel<<<n, 128, 0, st>>>(g.eq + toff * qd, g.tokens_d, qd, g.hp.n_vocab, g.q);
+    gather_rows_kernel<<<n, 128, 0, st>>>(g.ek + toff * kd, g.tokens_d, kd, g.hp.n_vocab, g.k);
+    gather_rows_kernel<<<n, 128, 0, st>>>(g.ev + toff * kd, g.tokens_d, kd, g.hp.n_vocab, g.v);
+    g.ctx->launches += 3;
+    const hl_attn_shape s = shape_for_layer(l);
+    hl_view qv{g.q, HL_DTYPE_F32, qd, g.hp.head_dim, 1}, kv_{g.k, HL_DTYPE_F32, kd, g.hp.head_dim, 1},
+        vv{g.v, HL_DTYPE_F32, kd, g.hp.head_dim, 1}, ov{g.out + l * layer_stride, HL_DTYPE_F32, qd, g.hp.head_dim, 1};
+    if (decode) {
+      B_TRY(hl_b200_kv_append_batch(g.ctx, kv, l, &s, &kv_, &vv, 1, g.ctx_len_d, g.table_d, g.table_len));
+      B_TRY(hl_b200_attn_decode(g.ctx, kv, l, &s, &qv, 1, g.ctx_len_d, pos0 + 1, g.table_d, g.table_len, &ov, nullptr));
+    } else {
+      B_TRY(hl_b200_kv_append_seq(g.ctx, kv, l, &s, &kv_, &vv, n, pos0, g.table_d, g.table_len));
+      B_TRY(hl_b200_attn_prefill(g.ctx, kv, l, &s, &qv, n, pos0, g.table_d, g.table_len, &ov, nullptr));
+    }
+  }
+  const int threads = 256;
+  logits_kernel<<<(g.hp.n_vocab + threads - 1) / threads, threads, qd * sizeof(float), st>>>(
+      g.out + static_cast<int64_t>(n - 1) * qd, g.hp.n_layer, layer_stride, qd, g.wout, g.hp.n_vocab, g.logits_d);
+  g.ctx->launches += 1;
+  B_CUDA(cudaGetLastError());
+  return HL_OK;
+}
+
+// One synchronisation per forward call, like the reference (naive.nim:4584, 5081): the result
+// copy queued by the caller and the device status word arrive together.
+int32_t finish_status() {
+  B_CUDA(cudaMemcpyAsync(g.status_h, g.ctx->status_d, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, g.ctx->stream));
+  B_CUDA(cudaStreamSynchronize(g.ctx->stream));
+  if (g.status_h[0] != 0) {
+    const int32_t code = g.status_h[0];
+    cudaMemset(g.ctx->status_d, 0, 2 * sizeof(int32_t));
+    return bfail(code, code == HL_ERR_TIMEOUT ? "a bounded device-side wait gave up during the forward pass"
+                                              : "a device-side index check failed during the forward pass");
+  }
+  return HL_OK;
+}
+
+int32_t check_cache(const hl_kv_cache* cache) {
+  if (!g.loaded) return bfail(HL_ERR_ARG, "no model loaded (loadModelBackend)");
+  if (!cache || !cache->gpu_cache) return bfail(HL_ERR_ARG, "null KV cache (initKvCache)");
+  return HL_OK;
+}
+
+}  // namespace
+
+extern "C" const char* hl_backend_last_error(void) { return g.err.c_str(); }
+extern "C" int64_t hl_backend_launch_count(void) { return g.ctx ? g.ctx->launches : 0; }
+
+extern "C" int32_t hl_backend_init_kv_cache(int32_t device, const hl_hparams* hp, int32_t max_len, hl_kv_cache* out) {
+  if (!out) return bfail(HL_ERR_ARG, "null cache");
+  B_PASS(check_hp(hp));
+  if (max_len <= 0) return bfail(HL_ERR_ARG, "max_len must be positive");
+  B_PASS(ensure_ctx(device));
+  const int bt = 16;
+  const int nb = (max_len + bt - 1) / bt;
+  hl_kv* kv = nullptr;
+  B_TRY(hl_b200_kv_create(g.ctx, hp->n_layer, hp->n_head_kv, hp->head_dim, bt, nb, &kv));
+  if (g.table_len < nb) {
+    if (g.table_d) cudaFree(g.table_d);
+    g.table_d = nullptr;
+    std::vector<int32_t> ident(nb);
+    for (int i = 0; i < nb; ++i) ident[i] = i;
+    B_CUDA(cudaMalloc(&g.table_d, nb * sizeof(int32_t)));
+    B_CUDA(cudaMemcpy(g.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice));
+  }
+  g.table_len = nb;
+  out->cur_len = 0;
+  out->max_len = max_len;
+  out->n_head_kv = hp->n_head_kv;
+  out->head_dim = hp->head_dim;
+  out->gpu_cache = kv;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_free_kv_cache(hl_kv_cache* cache) {
+  if (!cache || !cache->gpu_cache || !g.ctx) return bfail(HL_ERR_ARG, "null cache");
+  hl_b200_kv_destroy(g.ctx, static_cast<hl_kv*>(cache->gpu_cache));
+  cache->gpu_cache = nullptr;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_load_model(int32_t device, const hl_hparams* hp, const hl_standin_weights* w) {
+  B_PASS(check_hp(hp));
+  if (!w || !w->eq || !w->ek || !w->ev || !w->wout) return bfail(HL_ERR_ARG, "null weights");
+  if (g.loaded) return bfail(HL_ERR_ARG, "a model is already loaded (one model per process)");
+  B_PASS(ensure_ctx(device));
+  B_CUDA(cudaSetDevice(device));
+  g.hp = *hp;
+  const size_t qd = static_cast<size_t>(hp->n_head) * hp->head_dim, kd = static_cast<size_t>(hp->n_head_kv) * hp->head_dim;
+  const size_t lv = static_cast<size_t>(hp->n_layer) * hp->n_vocab;
+  auto up = [&](float** dst, const float* src, size_t n) -> bool {
+    return cudaMalloc(dst, n * sizeof(float)) == cudaSuccess &&
+           cudaMemcpy(*dst, src, n * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess;
+  };
+  bool ok = up(&g.eq, w->eq, lv * qd) && up(&g.ek, w->ek, lv * kd) && up(&g.ev, w->ev, lv * kd) &&
+            up(&g.wout, w->wout, qd * hp->n_vocab);
+  if (ok && w->q_norm) ok = up(&g.qn, w->q_norm, static_cast<size_t>(hp->n_layer) * hp->head_dim);
+  if (ok && w->k_norm) ok = up(&g.kn, w->k_norm, static_cast<size_t>(hp->n_layer) * hp->head_dim);
+  ok = ok && cudaMalloc(&g.logits_d, hp->n_vocab * sizeof(float)) == cudaSuccess &&
+       cudaMalloc(&g.ctx_len_d, sizeof(int32_t)) == cudaSuccess && cudaMalloc(&g.next_d, sizeof(int32_t)) == cudaSuccess &&
+       cudaMallocHost(&g.status_h, 2 * sizeof(int32_t)) == cudaSuccess && cudaEventCreate(&g.e0) == cudaSuccess &&
+       cudaEventCreate(&g.e1) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    g.loaded = true;  // so that unload frees the partial state
+    hl_backend_unload_model();
+    return bfail(HL_ERR_CUDA, "weight upload failed");
+  }
+  // theta table on the host, as ensureModelGpuPtrs does (naive.nim:3850-3861)
+  const int rope_dim = hp->rope_dim > 0 ? hp->rope_dim : hp->head_dim;
+  std::vector<float> theta(rope_dim / 2);
+  B_TRY(hl_b200_theta_table_h(hp->rope_freq_base, rope_dim, theta.data()));
+  if (hp->llama3_scaling) B_TRY(hl_b200_theta_llama3_scale_h(theta.data(), rope_dim / 2, 32.f, 1.f, 4.f, 8192));
+  B_TRY(hl_b200_set_rope(g.ctx, theta.data(), rope_dim / 2));
+  g.loaded = true;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_unload_model(void) {
+  if (!g.ctx) return HL_OK;
+  cudaSetDevice(g.device);
+  cudaStreamSynchronize(g.ctx->stream);
+  for (float** p : {&g.eq, &g.ek, &g.ev, &g.wout, &g.qn, &g.kn, &g.q, &g.k, &g.v, &g.out, &g.logits_d}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  for (int32_t** p : {&g.tokens_d, &g.ctx_len_d, &g.table_d, &g.next_d}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  if (g.status_h) cudaFreeHost(g.status_h);
+  g.status_h = nullptr;
+  if (g.e0) cudaEventDestroy(g.e0);
+  if (g.e1) cudaEventDestroy(g.e1);
+  g.e0 = g.e1 = nullptr;
+  g.act_cap = g.tokens_cap = g.table_len = 0;
+  g.loaded = false;
+  hl_b200_destroy(g.ctx);
+  g.ctx = nullptr;
+  g.device = -1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h) {
+  B_PASS(check_cache(cache));
+  if (!tokens_h || !logits_h) return bfail(HL_ERR_ARG, "null argument");
+  if (n <= 0) return bfail(HL_ERR_ARG, "prefill requires at least one token");
+  if (n > cache->max_len) return bfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
+  B_PASS(forward(tokens_h, n, 0, cache, false));
+  B_CUDA(cudaMemcpyAsync(logits_h, g.logits_d, g.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, g.ctx->stream));
+  B_PASS(finish_status());
+  cache->cur_len = n;
+  return HL_OK;
+}
+
+static int32_t decode_common(int32_t token, hl_kv_cache* cache) {
+  B_PASS(check_cache(cache));
+  if (cache->cur_len >= cache->max_len) return bfail(HL_ERR_CAPACITY, "KV cache full");
+  if (cache->cur_len < 0) return bfail(HL_ERR_ARG, "negative cur_len");
+  return forward(&token, 1, cache->cur_len, cache, true);
+}
+
+extern "C" int32_t hl_backend_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h) {
+  if (!logits_h) return bfail(HL_ERR_ARG, "null logits");
+  B_PASS(decode_common(token, cache));
+  B_CUDA(cudaMemcpyAsync(logits_h, g.logits_d, g.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, g.ctx->stream));
+  B_PASS(finish_status());
+  cache->cur_len += 1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token,
+                                                         float* gpu_ms) {
+  if (!next_token) return bfail(HL_ERR_ARG, "null next_token");
+  B_PASS(check_cache(cache));
+  if (gpu_ms) B_CUDA(cudaEventRecord(g.e0, g.ctx->stream));
+  B_PASS(decode_common(token, cache));
+  argmax_first_kernel<<<1, 256, 0, g.ctx->stream>>>(g.logits_d, g.hp.n_vocab, g.next_d);
+  g.ctx->launches += 1;
+  if (gpu_ms) B_CUDA(cudaEventRecord(g.e1, g.ctx->stream));
+  B_CUDA(cudaMemcpyAsync(next_token, g.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, g.ctx->stream));
+  B_PASS(finish_status());
+  if (gpu_ms) B_CUDA(cudaEventElapsedTime(gpu_ms, g.e0, g.e1));
+  cache->cur_len += 1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_forward_decode_token(int32_t token, hl_kv_cache* cache, int32_t* next_token) {
+  return hl_backend_forward_decode_token_timed(token, cache, next_token, nullptr);
+}

@@ -1,0 +1,83 @@
+/*
+ * hl_backend -- the reference's backend contract, as a C ABI over the B200 attention path.
+ *
+ * hippo_leap selects a backend at compile time (src/hippo_leap/inference.nim:7-14) and calls
+ * seven procs on it.  Each entry point below is the C side of one of them; the Nim module
+ * src/hippo_leap/backends/b200.nim binds them with importc and keeps the Nim signatures.
+ * Like the reference backends, the state is one model per process (module-level singletons,
+ * src/hippo_leap/backends/naive.nim:235-239) and callers serialise their calls.
+ *
+ * The model behind this contract here is an ATTENTION-ONLY stand-in: the projection, FFN and
+ * vocabulary layers of a real model are outside the hot path, so per layer the token id selects
+ * a query / key / value row from seeded tables (in place of embedding + Q/K/V projections),
+ * the layers' attention outputs are summed, and one [q_dim, n_vocab] matrix maps the sum to
+ * logits.  Everything between those -- QK-norm, RoPE, KV append, causal GQA prefill, split-KV
+ * decode -- is the product path, driven exactly as forwardPrefill / forwardDecode drive it.
+ *
+ * Status codes are hl_status (hl_b200.h); 0 = ok.  Nothing throws or aborts.
+ */
+#ifndef HL_BACKEND_H_
+#define HL_BACKEND_H_
+
+#include <stdint.h>
+
+#include "hl_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The HParams fields that parameterise the path (src/hippo_leap/model.nim:24-50). */
+typedef struct hl_hparams {
+  int32_t n_vocab, n_layer, n_head, n_head_kv, head_dim, rope_dim;
+  float rope_freq_base, rms_eps;
+  int32_t rope_mode;      /* HL_ROPE_SPLIT_HALF for the drop-in (what the reference GPU path does) */
+  int32_t llama3_scaling; /* non-zero: apply the llama3 frequency scaling to the theta table */
+} hl_hparams;
+
+/* Host float32 weights of the stand-in model. */
+typedef struct hl_standin_weights {
+  const float* eq;     /* [n_layer][n_vocab][n_head * head_dim]     token -> query row */
+  const float* ek;     /* [n_layer][n_vocab][n_head_kv * head_dim]  token -> key row   */
+  const float* ev;     /* [n_layer][n_vocab][n_head_kv * head_dim]  token -> value row */
+  const float* wout;   /* [n_head * head_dim][n_vocab]                                  */
+  const float* q_norm; /* [n_layer][head_dim] or NULL (attn_q_norm.weight)              */
+  const float* k_norm; /* [n_layer][head_dim] or NULL (attn_k_norm.weight)              */
+} hl_standin_weights;
+
+/* The KvCache fields the contract reads and writes (src/hippo_leap/backend_types.nim:41-49).
+ * Callers may reset cur_len to 0 between requests (src/hippo_leap/inference.nim:58). */
+typedef struct hl_kv_cache {
+  int32_t cur_len, max_len, n_head_kv, head_dim;
+  void* gpu_cache; /* hl_kv*: the paged pool; GpuKvCache.k/v[layer] come from hl_b200_kv_layer */
+} hl_kv_cache;
+
+/* initKvCache(hp, maxLen): src/hippo_leap/backends/naive.nim:3912-3931. */
+int32_t hl_backend_init_kv_cache(int32_t device, const hl_hparams* hp, int32_t max_len, hl_kv_cache* out);
+int32_t hl_backend_free_kv_cache(hl_kv_cache* cache);
+/* loadModelBackend(m, hp): naive.nim:3956-3958 (weight upload + theta table, naive.nim:3850-3861). */
+int32_t hl_backend_load_model(int32_t device, const hl_hparams* hp, const hl_standin_weights* w);
+/* unloadModelBackend(): naive.nim:3960-3962. */
+int32_t hl_backend_unload_model(void);
+/* forwardPrefill(m, tokens, cache) -> logits of the LAST position, [1, n_vocab] like the
+ * megakernel backend (megakernel.nim:2498); argmaxLast accepts that shape (sampling.nim:20-31).
+ * Like the reference it always starts at position 0 and leaves cache.cur_len = n
+ * (naive.nim:4075-4076, 4586-4587).  Errors as naive.nim:3969-3976: empty prompt, prompt longer
+ * than the cache. */
+int32_t hl_backend_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
+/* forwardDecode(m, token, cache): naive.nim:4592-5100.  pos = cache.cur_len; "KV cache full"
+ * when pos >= max_len (naive.nim:4598-4599). */
+int32_t hl_backend_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
+/* forwardDecodeToken(m, token, cache): naive.nim:5102-5546 (argmax on the device, 4-byte download). */
+int32_t hl_backend_forward_decode_token(int32_t token, hl_kv_cache* cache, int32_t* next_token);
+/* forwardDecodeTokenTimed(m, token, cache, gpuMs): megakernel.nim:2514-2529. */
+int32_t hl_backend_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token,
+                                              float* gpu_ms);
+const char* hl_backend_last_error(void);
+/* Kernel launches issued by the backend's context so far. */
+int64_t hl_backend_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HL_BACKEND_H_ */

@@ -31,9 +31,13 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_binding_table_covers_the_header():
+    from hippo_leap_b200 import backend
     declared = set(re.findall(r"\b(hl_b200_\w+)\s*\(", _header_text()))
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    declared_b = set(re.findall(r"\b(hl_backend_\w+)\s*\(", _header_text()))
+    assert declared_b == set(backend.BACKEND_SYMBOLS), declared_b ^ set(backend.BACKEND_SYMBOLS)
     _lib.load()
+    backend._lib()
 
 
 def test_status_and_enum_values_match_header():

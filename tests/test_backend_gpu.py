@@ -1,0 +1,139 @@
+"""The reference's drive pattern (tests/integration_inference.nim:34-46) through the backend contract:
+reset curLen, one prefill, argmax, N decode steps feeding the argmax back; the token id stream from
+the CUDA path must equal the oracle's, and the contract's errors must match the reference's."""
+import numpy as np
+import pytest
+
+import hippo_leap_b200 as hl
+import oracle
+from hippo_leap_b200 import backend as B
+from tests.helpers import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+class OracleModel:
+    """CPU restatement of the stand-in model on top of the oracle's attention path."""
+
+    def __init__(self, m: B.Model, max_len: int, rope_mode: int):
+        hp = m.hparams
+        self.m, self.hp, self.mode = m, hp, rope_mode
+        th = oracle.theta_table(hp.ropeDim or hp.headDim, hp.ropeFreqBase)
+        self.theta = hl.theta_llama3_scale(th) if hp.llama3Scaling else th
+        self.caches = [oracle.SeqCache(max_len, hp.nHeadKv, hp.headDim) for _ in range(hp.nLayer)]
+
+    def reset(self):
+        for c in self.caches:
+            c.cur_len = 0
+
+    def forward(self, tokens):
+        hp, m = self.hp, self.m
+        toks = np.asarray(tokens, np.int64)
+        x = None
+        for l in range(hp.nLayer):
+            q = m.eq[l][toks].reshape(len(toks), hp.nHead, hp.headDim)
+            k = m.ek[l][toks].reshape(len(toks), hp.nHeadKv, hp.headDim)
+            v = m.ev[l][toks].reshape(len(toks), hp.nHeadKv, hp.headDim)
+            rows = np.array([[len(toks) - 1, h] for h in range(hp.nHead)], np.int32)
+            o = oracle.attn_forward(q, k, v, self.caches[l], theta=self.theta, rope_mode=self.mode,
+                                    q_norm_w=None if m.qNorm is None else m.qNorm[l],
+                                    k_norm_w=None if m.kNorm is None else m.kNorm[l], eps=hp.rmsEps, rows=rows)
+            o = o.reshape(-1)
+            x = o if x is None else (x + o).astype(np.float32)
+        return oracle.matmul(x[None, :], m.wout)  # [1, nVocab]
+
+
+def _drive(hp, qk_norm, prompt_len, steps, seed):
+    m = B.standin_model(hp, seed, qk_norm)
+    max_len = prompt_len + steps + 3
+    cache = B.initKvCache(hp, max_len)
+    B.loadModelBackend(m, hp)
+    ref = OracleModel(m, max_len, hp.ropeMode)
+    try:
+        prompt = np.random.Generator(np.random.PCG64([seed, 1])).integers(0, hp.nVocab, prompt_len).astype(np.int32)
+        cache.curLen = 0
+        logits = B.forwardPrefill(m, prompt, cache)
+        want = ref.forward(prompt)
+        assert cache.curLen == prompt_len
+        assert_parity(logits, want, "prefill logits", max_abs_tol=2e-3 * float(np.abs(want).max()), rel_l2_tol=1e-3)
+        tok, rtok = B.argmaxLast(logits, hp.nVocab), B.argmaxLast(want, hp.nVocab)
+        got_stream, want_stream, margins = [tok], [rtok], []
+        for i in range(steps):
+            if i % 3 == 0:
+                logits = B.forwardDecode(m, tok, cache)
+                tok = B.argmaxLast(logits, hp.nVocab)
+            elif i % 3 == 1:
+                tok = B.forwardDecodeToken(m, tok, cache)
+            else:
+                tok, ms = B.forwardDecodeTokenTimed(m, tok, cache)
+                assert ms > 0
+            want = ref.forward([rtok])
+            top2 = np.sort(want[0])[-2:]
+            margins.append(float(top2[1] - top2[0]))
+            rtok = B.argmaxLast(want, hp.nVocab)
+            got_stream.append(tok)
+            want_stream.append(rtok)
+            if tok != rtok:
+                break
+        assert got_stream == want_stream, (
+            f"greedy stream diverged at step {len(got_stream) - 1}: got {got_stream[-1]}, oracle {want_stream[-1]}, "
+            f"oracle top-2 margin {margins[-1]:.3e}")
+        assert cache.curLen == prompt_len + steps
+        return m, cache
+    except BaseException:
+        B.freeKvCache(cache)
+        B.unloadModelBackend()
+        raise
+
+
+def test_greedy_stream_config1_tinyllama_shape():
+    """Config 1: 32/4 heads, hd 64, theta 1e4, 128-token prompt, 32 greedy steps, split-half RoPE (the
+    pairing of the reference GPU backends whose token stream the drop-in must reproduce)."""
+    hp = B.HParams(nVocab=512, nLayer=1, nHead=32, nHeadKv=4, headDim=64, ropeFreqBase=1e4)
+    m, cache = _drive(hp, False, 128, 32, seed=0)
+    # contract errors, as the reference raises them
+    with pytest.raises(ValueError, match="at least one token"):
+        B.forwardPrefill(m, [], cache)
+    with pytest.raises(ValueError, match="exceeds KV cache capacity"):
+        B.forwardPrefill(m, np.zeros(cache.maxLen + 1, np.int32), cache)
+    cache.curLen = cache.maxLen
+    with pytest.raises(ValueError, match="KV cache full"):
+        B.forwardDecode(m, 1, cache)
+    # an external reset of curLen starts a new request (inference.nim:58)
+    cache.curLen = 0
+    a = B.forwardPrefill(m, [5, 6, 7], cache)
+    cache.curLen = 0
+    b = B.forwardPrefill(m, [5, 6, 7], cache)
+    assert np.array_equal(a, b) and cache.curLen == 3
+    assert B.launchCount() > 0
+    B.freeKvCache(cache)
+    B.unloadModelBackend()
+    with pytest.raises(ValueError, match="no model loaded"):
+        B.forwardDecode(m, 1, cache)
+
+
+def test_greedy_stream_interleaved_rope_tensor_nim_pairing():
+    """Same drive with the CPU op's interleaved pairing (tensor.nim:156-166)."""
+    hp = B.HParams(nVocab=512, nLayer=1, nHead=32, nHeadKv=4, headDim=64, ropeFreqBase=1e4,
+                   ropeMode=hl.HL_ROPE_INTERLEAVED)
+    m, cache = _drive(hp, False, 128, 32, seed=3)
+    B.freeKvCache(cache)
+    B.unloadModelBackend()
+
+
+def test_greedy_stream_multilayer_llama3_scaled_theta_and_qk_norm():
+    """Several layers, llama3-scaled theta, hd 128 with QK-norm: 4 layers, 300-token prompt, 40 steps."""
+    hp = B.HParams(nVocab=512, nLayer=4, nHead=16, nHeadKv=4, headDim=128, ropeFreqBase=5e5, llama3Scaling=True)
+    m, cache = _drive(hp, True, 300, 40, seed=5)
+    B.freeKvCache(cache)
+    B.unloadModelBackend()
+
+
+def test_bad_hparams_rejected_before_any_launch():
+    hp = B.HParams(nVocab=64, nLayer=1, nHead=6, nHeadKv=4, headDim=64)
+    with pytest.raises(ValueError, match="divisible"):
+        B.initKvCache(hp, 32)
+    hp = B.HParams(nVocab=64, nLayer=1, nHead=4, nHeadKv=4, headDim=96)
+    with pytest.raises(ValueError, match="head_dim"):
+        B.initKvCache(hp, 32)
+    B.unloadModelBackend()
