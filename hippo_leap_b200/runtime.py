@@ -233,3 +233,18 @@ class Context:
             _i32_dev(block_tables), block_tables.shape[1], self._host_ptr(out_h),
             C.byref(ms) if timed else None))
         return ms.value if timed else None
+
+    def attn_decode_static(self, kv: KvPool, layer: int, shape: AttnShape, q, ctx_lens: torch.Tensor,
+                           max_ctx: int, block_tables: torch.Tensor, out: torch.Tensor):
+        """hl_b200_attn_decode_static: the decode step with no allocation inside the library.
+
+        For serving loops that own all device memory or cannot stall on cudaMalloc: the split-KV
+        scratch is a fixed array in the library (limit: batch * n_head * chunks <= 32768, else
+        HlError/HL_ERR_CAPACITY).  ``out`` must be supplied by the caller.  Calls share the scratch:
+        do not let two of them overlap on the GPU.  Make the first call per device at start-up.
+        """
+        sc, qc, oc = shape.c(), view_of(q), view_of(out)
+        self._check(self.lib.hl_b200_attn_decode_static(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], _i32_dev(ctx_lens),
+            max_ctx, _i32_dev(block_tables), block_tables.shape[1], C.byref(oc)))
+        return out

@@ -156,6 +156,20 @@ int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
                             int32_t max_ctx_h, const int32_t* block_tables,
                             int32_t max_blocks_per_seq, const hl_view* out, float* gpu_ms);
 
+/* No counterpart in the reference.  hl_b200_attn_decode without any allocation, for callers that have
+ * given all device memory to their own pool or cannot take the device-wide synchronisation of
+ * cudaMalloc / cudaFree inside the decode loop.  Same arguments and result as hl_b200_attn_decode
+ * (no gpu_ms); the split-KV partials live in a fixed 16.25 MiB array inside the library image, held
+ * by every GPU that loads the library until the process exits.  Limit: batch * n_head * chunks <=
+ * 32768 partial slots (chunks = ceil(max_ctx_h / chunk_tokens), 64..1024 tokens per chunk); beyond it
+ * the call returns HL_ERR_CAPACITY and launches nothing.  All calls on one GPU share the array: calls
+ * whose kernels overlap on the GPU race, so serialise them.  The first call on each device resolves
+ * the array's device address and configures the kernel; make it before any stream capture starts. */
+int32_t hl_b200_attn_decode_static(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                   const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                                   int32_t max_ctx_h, const int32_t* block_tables,
+                                   int32_t max_blocks_per_seq, const hl_view* out);
+
 /* ---- host-buffer forms ------------------------------------------------------------------
  * The same two steps for callers whose activations live in HOST memory (float32, token-major
  * contiguous: q [n][n_head][head_dim], k and v [n][n_head_kv][head_dim], out like q).  Each call
