@@ -152,7 +152,7 @@ def cpu_decode_sample(cfg, n_seq, steps, n_threads):
     return times, ctx_lens
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank, world, result_out):
     """The reference arm: the CPU restatement of the reference's float32 ops (the reference itself is
     Nim and cannot be built here), all host threads, on a bounded sample of the same workload."""
     if rank != 0:
@@ -161,12 +161,16 @@ def run_reference(args, rank, world):
     from hippo_leap_b200 import synth
 
     cfg = synth.CONFIGS[4]
-    n_threads = oracle.max_threads()
-    n_seq = 16
+    n_threads = os.cpu_count() or oracle.max_threads()  # torchrun pins OMP_NUM_THREADS=1; ask for all cores
+    # Size the per-step sample so that the whole run stays within about two minutes.
+    probe, _ = cpu_decode_sample(cfg, 4, 2, n_threads)
+    per_seq = probe[1] / 4
+    n_seq = int(max(1, min(16, 120.0 / ((args.warmup + args.steps) * per_seq))))
     times, ctx_lens = cpu_decode_sample(cfg, n_seq, args.warmup + args.steps, n_threads)
     t = sum(times[args.warmup:])
     value = n_seq * args.steps / t
-    sample = f"first {n_seq} of the 64 seeded sequences (ctx sum {int(ctx_lens.sum())}), one layer, {args.steps} steps"
+    sample = (f"first {n_seq} of the 64 seeded sequences (ctx sum {int(ctx_lens.sum())}), one layer, "
+              f"{args.steps} steps, {n_threads} threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
@@ -175,7 +179,7 @@ def run_reference(args, rank, world):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": n_threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=result_out, flush=True)
 
 
 def workload_config(cfg, n_gpus):
@@ -289,10 +293,20 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
             "scaling": "strong"}
 
 
+def _protect_stdout():
+    """Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
+    there.  Point fd 1 at stderr for the run and keep the real stdout for the result line."""
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(real, "w")
+
+
 def main():
+    result_out = _protect_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill side measurements")
@@ -305,7 +319,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, result_out)
         return
 
     import torch
@@ -341,7 +355,6 @@ def main():
     l0 = ctx.launch_count()
     ms_local = timed_loop(torch, step, args.steps)
     launches = ctx.launch_count() - l0
-    clocks = sampler.stop()
     t = torch.tensor([ms_local], device=device, dtype=torch.float64)
     if world > 1:
         dist.barrier()
@@ -379,6 +392,7 @@ def main():
     e2e_value = world * B * args.steps / (float(t2.item()) * 1e-3)
     h2d = q_h.numel() * 4 + k_h.numel() * 4 + v_h.numel() * 4
     d2h = out_h.numel() * 4
+    clocks = sampler.stop()  # sampled across the three timed loops above (device, kernel-only, end-to-end)
     code, detail = ctx.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) after the timed region")
@@ -393,8 +407,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        import oracle
-        n_threads = oracle.max_threads()
+        n_threads = os.cpu_count() or 1
         n_seq = 16
         times, cl = cpu_decode_sample(cfg, n_seq, 3, n_threads)
         tt = sum(times[1:]) / 2
@@ -413,7 +426,7 @@ def main():
                     "ms_per_step": float(t2.item()) / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
         }
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=result_out, flush=True)
     w["kv"].destroy()
     ctx.close()
     if world > 1:
