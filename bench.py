@@ -249,10 +249,12 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     import hippo_leap_b200 as hl
     from hippo_leap_b200 import synth
 
+    from hippo_leap_b200 import sharding
+
     cfg = synth.CONFIGS[5]
     S = cfg.prefill
-    hkv_l = cfg.n_head_kv // world
-    hq_l = cfg.n_head // world
+    sh = sharding.head_shard(rank, world, cfg.n_head, cfg.n_head_kv)
+    hkv_l, hq_l = sh.n_head_kv, sh.n_head
     gen = torch.Generator(device=device)
     gen.manual_seed(3000 + rank)
     shape = hl.AttnShape(hq_l, hkv_l, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
@@ -272,7 +274,7 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     def step():
         ctx.attn_prefill(kv, 0, shape, q, 0, table, out_l.permute(1, 0, 2))
         if world > 1:
-            dist.all_gather_into_tensor(full, out_l)
+            sharding.gather_heads(out_l, full)
 
     for _ in range(2):
         step()
