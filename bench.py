@@ -200,13 +200,13 @@ def timed_loop(torch, fn, steps):
     return e0.elapsed_time(e1)  # ms
 
 
-def extras_single_gpu(ctx, torch, device, peaks, quick):
+def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
     """Prefill TFLOP/s on the prefill configurations (one layer each), device-resident inputs."""
     import hippo_leap_b200 as hl
     from hippo_leap_b200 import synth
 
     res = {}
-    for ci in (2, 3, 5):
+    for ci in configs:
         cfg = synth.CONFIGS[ci]
         S = cfg.prefill
         gen = torch.Generator(device=device)
@@ -314,6 +314,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="CFG",
+                    help="measure only the prefill kernel of configuration 2, 3 or 5 (small profiling target)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -339,6 +341,11 @@ def main():
     peaks = load_peaks()
     cfg = synth.CONFIGS[4]
     ctx = hl.Context(local_rank, torch.cuda.current_stream())
+    if args.prefill_only:
+        res = extras_single_gpu(ctx, torch, device, peaks, quick=True, configs=(args.prefill_only,))
+        print(json.dumps(res), file=result_out, flush=True)
+        ctx.close()
+        return
     ctx.set_tuning(args.decode_chunk, 0)
     w = setup_decode(ctx, cfg, rank, device)
     B = len(w["ctx_lens"])

@@ -113,6 +113,12 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // Shared-memory matrix descriptors (sm_100 format): start address, leading / stride byte offsets in
 // 16-byte units, version 1, 128-byte swizzle.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -138,7 +144,7 @@ struct PrefillTcCfg {
   static constexpr int kBarOff = kRowOff + 8 * HD * 4;
   static constexpr int kNumBars = 4 * kStages + 7;
   static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 16;
-  static constexpr int kThreads = 320;
+  static constexpr int kThreads = 384;  // 12 warps: two softmax warpgroups + one warpgroup holding the TMA and MMA warps
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS = 0, kColO = 256;  // S_t at t*128, O_t at 256 + t*HD
 };
@@ -156,7 +162,7 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, int32_t*
 }
 
 template <int HD>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
     attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                            PrefillTcArgs ta) {
   using Cfg = PrefillTcCfg<HD>;
@@ -222,8 +228,13 @@ __global__ void __launch_bounds__(320, 1)
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // Register budget: 384 threads x 168 registers.  The TMA / MMA warpgroup gives most of its share to
+  // the two softmax warpgroups, which hold a whole 128-column row of S per thread.
+  // (setmaxnreg sits at the top of each role's branch so that the compiler sees which limit governs
+  // which code.)
   if (warp == 8) {
     // ======================= TMA producer =======================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (lane == 0) {
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
@@ -266,6 +277,7 @@ __global__ void __launch_bounds__(320, 1)
     }
   } else if (warp == 9) {
     // ======================= MMA issuer =======================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(128, 128, 0);
       constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
@@ -322,8 +334,11 @@ __global__ void __launch_bounds__(320, 1)
       }
     }
     __syncwarp();
+  } else if (warp >= 10) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");  // idle warps of the third warpgroup
   } else {
     // ======================= softmax warps (tile t, row r) =======================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int t = warp >> 2;
     const int r = tid & 127;
     const int trow = t0 + 128 * t + r;          // token index of this thread's row
@@ -423,9 +438,22 @@ __global__ void __launch_bounds__(320, 1)
         for (int i = 0; i < 128; ++i)
           if (key0 + i > pos) s[i] = -INFINITY;
       }
-      float mx = s[0];
+      // row maximum: four independent chains of 3-input max (short dependency chains: one warp per
+      // scheduler runs this alone, so instruction-level parallelism is all the latency hiding there is)
+      float mx;
+      {
+        float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        for (int i = 4; i < 128; i += 8) {
+          m4[0] = max3(m4[0], s[i], s[i + 1]);
+          m4[1] = max3(m4[1], s[i + 2], s[i + 3]);
+          if (i + 4 < 128) {
+            m4[2] = max3(m4[2], s[i + 4], s[i + 5]);
+            m4[3] = max3(m4[3], s[i + 6], s[i + 7]);
+          }
+        }
+        mx = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
+      }
       if (j == 0) {
         m = mx;
       } else {
@@ -447,18 +475,20 @@ __global__ void __launch_bounds__(320, 1)
         }
       }
       const float mc = m * c;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[64];
 #pragma unroll
-      for (int i = 0; i < 128; i += 2) {
-        const float p0 = fast_exp2(fmaf(s[i], c, -mc));
-        const float p1 = fast_exp2(fmaf(s[i + 1], c, -mc));
-        sum += p0 + p1;
-        pk[i >> 1] = pack_half2(p0, p1);
+      for (int half_i = 0; half_i < 2; ++half_i) {
+#pragma unroll
+        for (int i = half_i * 64; i < half_i * 64 + 64; i += 2) {
+          const float p0 = fast_exp2(fmaf(s[i], c, -mc));
+          const float p1 = fast_exp2(fmaf(s[i + 1], c, -mc));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          pk[i >> 1] = pack_half2(p0, p1);
+        }
+        tc_st32(tS + half_i * 32, pk + half_i * 32);  // first half of P is on its way while the second is computed
       }
-      l += sum;
-      tc_st32(tS, pk);
-      tc_st32(tS + 32, pk + 32);
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
