@@ -119,6 +119,45 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
+// VEC consecutive dims of one head row (dim stride 1), as one vector load when the address allows.
+template <int VEC>
+__device__ __forceinline__ void load_vec(const View& v, int64_t t, int64_t h, int d0, float* x) {
+  const int64_t off = t * v.ts + h * v.hs + d0;
+  if (v.dtype == HL_DTYPE_F32) {
+    const float* p = static_cast<const float*>(v.ptr) + off;
+    if ((reinterpret_cast<uintptr_t>(p) & (VEC * 4 - 1)) == 0) {
+      if constexpr (VEC == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
+      } else {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        x[0] = q.x; x[1] = q.y;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x[e] = p[e];
+    }
+  } else {
+    const __half* p = static_cast<const __half*>(v.ptr) + off;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[e] = __half2float(p[e]);
+  }
+}
+
+// 2^x for x <= 0 on the FMA / integer pipes (Cody-Waite split + degree-3 polynomial, relative error
+// below 8e-5, far under the fp16 rounding P gets next).  A quarter of the softmax exponentials go
+// through this instead of the special-function unit, which is the busiest unit of the kernel.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float magic = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  const float xr = x + magic;
+  const float f = x - (xr - magic);  // in [-0.5, 0.5]
+  float p = fmaf(f, 0.05508868396282196f, 0.24260404706001282f);
+  p = fmaf(p, f, 0.6932762265205383f);
+  p = fmaf(p, f, 0.9999289512634277f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
 // Shared-memory matrix descriptors (sm_100 format): start address, leading / stride byte offsets in
 // 16-byte units, version 1, 128-byte swizzle.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -130,6 +169,10 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int b_mn_major) 
   return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
 }
+
+#ifndef HL_TC_POLY_MASK
+#define HL_TC_POLY_MASK (-1)  // -1: every exponential on the special-function unit; 3: a quarter on the FMA pipe; 7: an eighth
+#endif
 
 template <int HD>
 struct PrefillTcCfg {
@@ -353,62 +396,83 @@ __global__ void __launch_bounds__(384, 1)
       constexpr int VEC = HD / 32;
       const bool fast = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
       float* xrow = reinterpret_cast<float*>(gen + Cfg::kRowOff) + warp * HD;
-      for (int rr = 0; rr < 32; ++rr) {
-        const int row = (warp & 3) * 32 + rr;
-        const int tt = t0 + 128 * t + row;
-        const bool live = tt < a.n_tok;
-        if (fast) {
-          float x[VEC];
-          const int d0 = lane * VEC;
-          if (live) {
+      if (fast) {
+        // R rows per pass with all their global loads issued before any arithmetic: a warp that walked
+        // its 32 rows one dependent load at a time would spend most of the prologue waiting on HBM.
+        constexpr int R = 8;
+        const int d0 = lane * VEC;
+        const int last_pos = a.start_pos + a.n_tok - 1;
+        for (int rb = 0; rb < 32; rb += R) {
+          float x[R][VEC];
+          float2 cs[R][VEC];  // interleaved uses VEC/2 of them, split-half VEC
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) x[e] = view_load(a.q, tt, h, d0 + e);
-            if (a.q_norm_w != nullptr) {
+          for (int u = 0; u < R; ++u) {
+            const int tt = t0 + 128 * t + (warp & 3) * 32 + rb + u;
+            if (tt < a.n_tok) {
+              load_vec<VEC>(a.q, tt, h, d0, x[u]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
+            }
+            const float2* csr = ta.cs_table + static_cast<int64_t>(min(a.start_pos + tt, last_pos)) * (HD / 2);
+            if (a.rope_mode == HL_ROPE_INTERLEAVED) {
+#pragma unroll
+              for (int e = 0; e < VEC; e += 2) cs[u][e >> 1] = csr[(d0 + e) >> 1];
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) cs[u][e] = csr[(d0 + e) & (HD / 2 - 1)];
+            }
+          }
+          if (a.q_norm_w != nullptr) {
+            float w[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) w[e] = a.q_norm_w[d0 + e];
+#pragma unroll
+            for (int u = 0; u < R; ++u) {
               float ss = 0.f;
 #pragma unroll
-              for (int e = 0; e < VEC; ++e) ss += x[e] * x[e];
+              for (int e = 0; e < VEC; ++e) ss += x[u][e] * x[u][e];
 #pragma unroll
               for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
               const float inv = 1.0f / sqrtf(ss / static_cast<float>(HD) + a.eps);
 #pragma unroll
-              for (int e = 0; e < VEC; ++e) x[e] = x[e] * inv * a.q_norm_w[d0 + e];
+              for (int e = 0; e < VEC; ++e) x[u][e] = x[u][e] * inv * w[e];
             }
-            const float2* cs = ta.cs_table + static_cast<int64_t>(a.start_pos + tt) * (HD / 2);
+          }
+#pragma unroll
+          for (int u = 0; u < R; ++u) {
             if (a.rope_mode == HL_ROPE_INTERLEAVED) {
 #pragma unroll
               for (int e = 0; e < VEC; e += 2) {
-                const float2 c = cs[(d0 + e) >> 1];
-                const float v0 = x[e], v1 = x[e + 1];
-                x[e] = v0 * c.x - v1 * c.y;
-                x[e + 1] = v0 * c.y + v1 * c.x;
+                const float2 c = cs[u][e >> 1];
+                const float v0 = x[u][e], v1 = x[u][e + 1];
+                x[u][e] = v0 * c.x - v1 * c.y;
+                x[u][e + 1] = v0 * c.y + v1 * c.x;
               }
             } else {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) {
-                const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-                const int d = d0 + e;
-                if (d < HD / 2) {
-                  const float2 c = cs[d];
-                  x[e] = x[e] * c.x - other * c.y;
-                } else {
-                  const float2 c = cs[d - HD / 2];
-                  x[e] = other * c.y + x[e] * c.x;
-                }
+                const float other = __shfl_xor_sync(0xffffffffu, x[u][e], 16);
+                const float2 c = cs[u][e];
+                x[u][e] = (d0 + e < HD / 2) ? x[u][e] * c.x - other * c.y : other * c.y + x[u][e] * c.x;
               }
             }
-          } else {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+            const int row = (warp & 3) * 32 + rb + u;
+            const uint32_t addr = swz128(q_tile + (d0 >> 6) * Cfg::kHalfBytes, row, (d0 & 63) >> 3) + (d0 & 7) * 2;
+            if constexpr (VEC == 4) {
+              asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(pack_half2(x[u][0], x[u][1])),
+                           "r"(pack_half2(x[u][2], x[u][3]))
+                           : "memory");
+            } else {
+              asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack_half2(x[u][0], x[u][1])) : "memory");
+            }
           }
-          const uint32_t addr = swz128(q_tile + (d0 >> 6) * Cfg::kHalfBytes, row, (d0 & 63) >> 3) + (d0 & 7) * 2;
-          if constexpr (VEC == 4) {
-            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(pack_half2(x[0], x[1])),
-                         "r"(pack_half2(x[2], x[3]))
-                         : "memory");
-          } else {
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(pack_half2(x[0], x[1])) : "memory");
-          }
-        } else {
+        }
+      } else {
+        for (int rr = 0; rr < 32; ++rr) {
+          const int row = (warp & 3) * 32 + rr;
+          const int tt = t0 + 128 * t + row;
+          const bool live = tt < a.n_tok;
           if (live) {
 #pragma unroll
             for (int d = lane; d < HD; d += 32) xrow[d] = view_load(a.q, tt, h, d);
@@ -481,8 +545,9 @@ __global__ void __launch_bounds__(384, 1)
       for (int half_i = 0; half_i < 2; ++half_i) {
 #pragma unroll
         for (int i = half_i * 64; i < half_i * 64 + 64; i += 2) {
-          const float p0 = fast_exp2(fmaf(s[i], c, -mc));
-          const float p1 = fast_exp2(fmaf(s[i + 1], c, -mc));
+          const bool poly = HL_TC_POLY_MASK >= 0 && ((i >> 1) & HL_TC_POLY_MASK) == HL_TC_POLY_MASK;  // compile-time after unrolling
+          const float p0 = poly ? exp2_poly(fmaf(s[i], c, -mc)) : fast_exp2(fmaf(s[i], c, -mc));
+          const float p1 = poly ? exp2_poly(fmaf(s[i + 1], c, -mc)) : fast_exp2(fmaf(s[i + 1], c, -mc));
           sum4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = pack_half2(p0, p1);
         }
@@ -505,13 +570,27 @@ __global__ void __launch_bounds__(384, 1)
         tc_ld32f(tO + q4 * 32, oreg);
         tc_wait_ld();
         if (live) {
+          const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(h) * a.out.hs + q4 * 32;
           if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
-            __half* dst = static_cast<__half*>(const_cast<void*>(a.out.ptr)) + static_cast<int64_t>(trow) * a.out.ts +
-                          static_cast<int64_t>(h) * a.out.hs + q4 * 32;
+            __half* dst = static_cast<__half*>(const_cast<void*>(a.out.ptr)) + off;
+            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              *reinterpret_cast<uint32_t*>(dst + i) =
-                  pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+              for (int i = 0; i < 32; i += 8)
+                *reinterpret_cast<uint4*>(dst + i) =
+                    make_uint4(pack_half2(oreg[i] * inv, oreg[i + 1] * inv), pack_half2(oreg[i + 2] * inv, oreg[i + 3] * inv),
+                               pack_half2(oreg[i + 4] * inv, oreg[i + 5] * inv), pack_half2(oreg[i + 6] * inv, oreg[i + 7] * inv));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2)
+                *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+            }
+          } else if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F32 &&
+                     (reinterpret_cast<uintptr_t>(static_cast<const float*>(a.out.ptr) + off) & 15) == 0) {
+            float* dst = static_cast<float*>(const_cast<void*>(a.out.ptr)) + off;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) =
+                  make_float4(oreg[i] * inv, oreg[i + 1] * inv, oreg[i + 2] * inv, oreg[i + 3] * inv);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) view_store(a.out, trow, h, q4 * 32 + i, oreg[i] * inv);

@@ -161,7 +161,7 @@ def test_reference_dim_major_layout_and_fp16_output(hl_ctx):
     for kernel in (1, 2):
         hl_ctx.set_tuning(0, kernel)
         hl_ctx.attn_prefill(kv2, 0, shape, q_ds.permute(2, 0, 1), 0, tt, out_ds.permute(2, 0, 1))
-        assert float((out_ds.permute(2, 0, 1) - base).abs().max()) < 3e-4
+        assert float((out_ds.permute(2, 0, 1) - base).abs().max()) < 6e-4
         o16 = torch.empty((S, cfg.n_head, cfg.head_dim), dtype=torch.float16, device="cuda")
         hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt, o16)
         assert float((o16.float() - base).abs().max()) < 4e-3
