@@ -113,6 +113,26 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// Packed pairs of float32 (sm_100 has two-wide fp32 FMA / ADD): halves the issue slots of the
+// scale-and-subtract and of the row sum in the softmax.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -539,21 +559,28 @@ __global__ void __launch_bounds__(384, 1)
         }
       }
       const float mc = m * c;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t c2 = pack_f32x2(c, c), nmc2 = pack_f32x2(-mc, -mc);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four independent packed accumulators (bits of +0.0f pairs)
       uint32_t pk[64];
 #pragma unroll
       for (int half_i = 0; half_i < 2; ++half_i) {
 #pragma unroll
         for (int i = half_i * 64; i < half_i * 64 + 64; i += 2) {
-          const bool poly = HL_TC_POLY_MASK >= 0 && ((i >> 1) & HL_TC_POLY_MASK) == HL_TC_POLY_MASK;  // compile-time after unrolling
-          const float p0 = poly ? exp2_poly(fmaf(s[i], c, -mc)) : fast_exp2(fmaf(s[i], c, -mc));
-          const float p1 = poly ? exp2_poly(fmaf(s[i + 1], c, -mc)) : fast_exp2(fmaf(s[i + 1], c, -mc));
-          sum4[(i >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(s[i], s[i + 1]), c2, nmc2), x0, x1);
+          const bool poly = HL_TC_POLY_MASK >= 0 && ((i >> 1) & HL_TC_POLY_MASK) == HL_TC_POLY_MASK;  // compile-time
+          const float p0 = poly ? exp2_poly(x0) : fast_exp2(x0);
+          const float p1 = poly ? exp2_poly(x1) : fast_exp2(x1);
+          sum2[(i >> 1) & 3] = add_f32x2(sum2[(i >> 1) & 3], pack_f32x2(p0, p1));
           pk[i >> 1] = pack_half2(p0, p1);
         }
         tc_st32(tS + half_i * 32, pk + half_i * 32);  // first half of P is on its way while the second is computed
       }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float a0, a1;
+        unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
+        l += a0 + a1;
+      }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
