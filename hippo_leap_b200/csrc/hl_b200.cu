@@ -203,6 +203,33 @@ extern "C" int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, 
 }
 
 // ---------------------------------------------------------------------------------------------
+// bounded-wait self-test
+// ---------------------------------------------------------------------------------------------
+__global__ void selftest_timeout_kernel(int32_t* status, uint32_t max_polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);  // one arrival expected; none will ever come
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bool ok = false;
+    for (uint32_t i = 0; i < max_polls && !ok; ++i) ok = mbar_try_wait(&bar, 0);
+    if (!ok) report(status, HL_ERR_TIMEOUT, 900);
+  }
+}
+
+extern "C" int32_t hl_b200_selftest_wait_timeout(hl_ctx* ctx, int32_t max_polls) {
+  if (!ctx) return HL_ERR_ARG;
+  if (max_polls <= 0 || max_polls > (1 << 20)) return hl_fail(ctx, HL_ERR_ARG, "selftest: max_polls outside [1, 2^20]");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  selftest_timeout_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_d, static_cast<uint32_t>(max_polls));
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // RoPE table
 // ---------------------------------------------------------------------------------------------
 extern "C" int32_t hl_b200_theta_table_h(float base, int32_t rope_dim, float* theta_h) {

@@ -248,3 +248,7 @@ class Context:
             self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], _i32_dev(ctx_lens),
             max_ctx, _i32_dev(block_tables), block_tables.shape[1], C.byref(oc)))
         return out
+
+    def selftest_wait_timeout(self, max_polls: int = 1000):
+        """Launch the bounded-wait self-test; read the outcome with ``device_status()``."""
+        self._check(self.lib.hl_b200_selftest_wait_timeout(self.handle, max_polls))

@@ -72,3 +72,47 @@ def max_over_ranks(value: float, device) -> float:
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+class HeadShardedPrefill:
+    """Head-sharded causal prefill of one sequence with the all-gather of head outputs overlapped.
+
+    The query range is cut into ``n_chunks`` row chunks.  Chunks are computed from the LAST (most
+    keys, most work) to the FIRST (cheapest); as soon as a chunk's local heads are done its
+    all-gather starts on a side stream while the next chunk computes, so only the gather of the
+    cheapest chunk is exposed.  Result layout: ``[n_chunks][n_head][chunk_rows][head_dim]`` fp16
+    -- per chunk, rank-order concatenation of the head-major local outputs is the final layout.
+    K/V of the whole sequence must have been appended to this rank's KV pool slice before.
+    """
+
+    def __init__(self, ctx, kv, shape, n_tok: int, n_chunks: int, device, world: int | None = None):
+        if n_tok % n_chunks != 0:
+            raise ValueError("n_tok must divide into n_chunks")
+        self.ctx, self.kv, self.shape = ctx, kv, shape
+        self.n_tok, self.n_chunks, self.rows = n_tok, n_chunks, n_tok // n_chunks
+        self.world = world if world is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+        hd = shape.head_dim
+        self.local = torch.empty((n_chunks, shape.n_head, self.rows, hd), dtype=torch.float16, device=device)
+        self.full = torch.empty((n_chunks, shape.n_head * self.world, self.rows, hd), dtype=torch.float16,
+                                device=device)
+        self.comm_stream = torch.cuda.Stream(device=device)
+        self.events = [torch.cuda.Event() for _ in range(n_chunks)]
+
+    def run(self, q: torch.Tensor, block_table: torch.Tensor, layer: int = 0) -> torch.Tensor:
+        """q: [n_tok, n_head_local, hd] (this rank's query heads).  Returns the gathered tensor; the
+        caller's stream is made to wait for the last gather."""
+        main = torch.cuda.current_stream()
+        self.comm_stream.wait_stream(main)  # earlier readers of `full` on the main stream are done
+        for c in range(self.n_chunks - 1, -1, -1):
+            lo = c * self.rows
+            self.ctx.attn_prefill(self.kv, layer, self.shape, q[lo:lo + self.rows], lo, block_table,
+                                  self.local[c].permute(1, 0, 2))
+            if self.world > 1:
+                self.events[c].record(main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(self.events[c])
+                    dist.all_gather_into_tensor(self.full[c], self.local[c])
+            else:
+                self.full[c].copy_(self.local[c])
+        main.wait_stream(self.comm_stream)
+        return self.full

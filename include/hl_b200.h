@@ -187,6 +187,12 @@ int32_t hl_b200_decode_step_host(hl_ctx* ctx, hl_kv* kv, int32_t layer,
                                  int32_t max_ctx_h, const int32_t* block_tables,
                                  int32_t max_blocks_per_seq, float* out_h, float* gpu_ms);
 
+/* No counterpart in the reference.  Self-test of the bounded-wait machinery: launches one CTA that
+ * waits, for at most `max_polls` polls, on a barrier nothing ever signals.  The wait gives up,
+ * the kernel returns normally, and hl_b200_device_status then reports {HL_ERR_TIMEOUT, 900}.  The
+ * context stays usable.  (How a lost signal would surface in the attention kernels, without one.) */
+int32_t hl_b200_selftest_wait_timeout(hl_ctx* ctx, int32_t max_polls);
+
 /* Tunables (0 = automatic): tokens per split-KV chunk for decode; which prefill kernel
  * runs (0 auto, 1 = warp-MMA kernel, 2 = tcgen05 kernel). */
 int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, int32_t prefill_kernel);

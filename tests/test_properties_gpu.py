@@ -206,3 +206,30 @@ def test_config4_batched_decode_sampled_parity(hl_ctx):
         want = oracle_seq(qn[i:i + 1], kk[-1:], vv[-1:], theta=theta, rope_mode=1, rows=rows, prefix=(kk[:-1], vv[:-1]))
         assert_parity(out[i, heads], want, f"config 4 sequence {i} (ctx {ctx_lens[i]})")
     kv.destroy()
+
+
+def test_head_sharded_prefill_runner_single_rank_equals_plain_prefill(hl_ctx):
+    """The chunked, overlapped head-sharded runner (world size 1 here: the gather is a copy) returns the
+    rows of one plain prefill call, in its [chunk][head][row][dim] layout."""
+    from hippo_leap_b200 import sharding
+    cfg = synth.CONFIGS[3]
+    S, bt = 2048, 128
+    q, k, v = synth.gen_qkv(cfg, S)
+    theta = cfg.theta()
+    hl_ctx.set_rope(theta)
+    shape = _shape_for(cfg, hl.HL_ROPE_SPLIT_HALF)
+    tq, tk, tv = _upload(q, k, v)
+    tt = torch.arange(S // bt, dtype=torch.int32, device="cuda")
+    kv = hl_ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, S // bt)
+    hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
+    plain = hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt)
+    runner = sharding.HeadShardedPrefill(hl_ctx, kv, shape, S, 4, tq.device, world=1)
+    full = runner.run(tq, tt)  # [4, H, 512, hd] fp16
+    torch.cuda.synchronize()
+    got = full.permute(0, 2, 1, 3).reshape(S, cfg.n_head, cfg.head_dim).float()
+    assert float((got - plain).abs().max()) < 4e-3  # fp16 output rounding only
+    rows = np.array([[5, 0], [700, 9], [2047, 31]], np.int32)
+    want = oracle_seq(q, k, v, theta=theta, rope_mode=1, rows=rows)
+    assert_parity(got[[5, 700, 2047], [0, 9, 31]].cpu().numpy(), want, "head-sharded runner rows",
+                  max_abs_tol=4e-3, rel_l2_tol=2e-3)  # fp16 OUTPUT variant: its own rounding on top of the path's
+    kv.destroy()
