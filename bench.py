@@ -244,6 +244,46 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
     return res
 
 
+def extra_config2_pipeline(torch, device_index):
+    """Config 2 end to end through the backend contract (the calls hippo_leap's generate loop makes):
+    one 2048-token prefill, then 256 greedy decode steps, 16 attention layers, llama3-scaled theta,
+    host token ids in, host logits / token id out, one synchronisation per call."""
+    from hippo_leap_b200 import backend as B
+    from hippo_leap_b200 import synth
+
+    cfg = synth.CONFIGS[2]
+    hp = B.HParams(nVocab=512, nLayer=cfg.layers, nHead=cfg.n_head, nHeadKv=cfg.n_head_kv, headDim=cfg.head_dim,
+                   ropeFreqBase=cfg.rope_base, llama3Scaling=True)
+    m = B.standin_model(hp, cfg.seed)
+    cache = B.initKvCache(hp, cfg.prefill + cfg.decode_steps + 8, device_index)
+    B.loadModelBackend(m, hp, device_index)
+    try:
+        prompt = np.random.Generator(np.random.PCG64([cfg.seed, 1])).integers(0, hp.nVocab, cfg.prefill).astype(np.int32)
+        res = {}
+        for rep in range(2):  # first pass warms up (allocations, cos/sin table), second is timed
+            cache.curLen = 0
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            tok = B.argmaxLast(B.forwardPrefill(m, prompt, cache), hp.nVocab)
+            t1 = time.perf_counter()
+            gpu_ms = 0.0
+            for _ in range(cfg.decode_steps):
+                tok, ms = B.forwardDecodeTokenTimed(m, tok, cache)
+                gpu_ms += ms
+            t2 = time.perf_counter()
+            res = {"workload": "config 2: Llama-3.2-1B attention shape, 16 layers, prefill 2048 + 256 greedy decode "
+                               "steps through the backend contract (attention-only stand-in model)",
+                   "prefill_ms": (t1 - t0) * 1e3, "prefill_tok_per_s": cfg.prefill / (t1 - t0),
+                   "decode_ms_per_token": (t2 - t1) * 1e3 / cfg.decode_steps,
+                   "decode_tok_per_s": cfg.decode_steps / (t2 - t1),
+                   "decode_gpu_ms_per_token": gpu_ms / cfg.decode_steps,
+                   "launches": B.launchCount()}
+        return res
+    finally:
+        B.freeKvCache(cache)
+        B.unloadModelBackend()
+
+
 def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     """Config 5 with KV heads split across ranks and one all-gather of the head outputs (fp16)."""
     import hippo_leap_b200 as hl
@@ -267,24 +307,31 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     k = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
     v = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
     ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
-    n_chunks = 4 if world > 1 else 1
-    runner = sharding.HeadShardedPrefill(ctx, kv, shape, S, n_chunks, device, world)
-
-    def step():
-        runner.run(q, table)
-
-    for _ in range(2):
-        step()
+    results = {}
+    fused = sharding.FusedHeadShardedPrefill(ctx, kv, shape, S, cfg.n_head, device)
+    plain = sharding.HeadShardedPrefill(ctx, kv, shape, S, 1, device, world)
+    for name, runner in (("fused_in_kernel", fused), ("nccl_allgather_after", plain)):
+        for _ in range(2):
+            runner.run(q, table)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        n = 5
+        results[name] = sharding.max_over_ranks(timed_loop(torch, lambda: runner.run(q, table), n) / n, device)
+    # cross-check: both ways must produce the same gathered tensor
+    a_ = fused.run(q, table)
+    b_ = plain.run(q, table)
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    n = 5
-    ms = sharding.max_over_ranks(timed_loop(torch, step, n) / n, device)
+    same = bool(torch.equal(a_, b_[0]))
+
+    ms = results["fused_in_kernel"]
     fl = synth.prefill_flops(cfg.n_head, cfg.head_dim, S)
     tf = fl / (ms * 1e-3) / 1e12
     kv.destroy()
-    return {"workload": f"{cfg.name}: 32768-token causal prefill, KV heads {hkv_l}/GPU, fp16 all-gather of head "
-                        f"outputs in {n_chunks} row chunks overlapped with compute",
+    return {"workload": f"{cfg.name}: 32768-token causal prefill, KV heads {hkv_l}/GPU, fp16 head outputs stored to "
+                        "every GPU by the attention kernel itself (peer stores over NVLink, no collective kernel)",
+            "ms_nccl_allgather_after": results["nccl_allgather_after"], "ms_fused_in_kernel": results["fused_in_kernel"],
+            "fused_equals_allgather": same,
             "ms": ms, "tflops_aggregate": tf, "frac_of_tensor_peak_per_gpu": tf / world / peaks["tflops"],
             "scaling": "strong"}
 
@@ -308,6 +355,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--pipeline-only", action="store_true", help="measure only the config 2 backend pipeline")
     ap.add_argument("--head-sharded-only", action="store_true",
                     help="measure only the head-sharded config 5 prefill + all-gather at N GPUs")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="CFG",
@@ -337,6 +385,10 @@ def main():
     peaks = load_peaks()
     cfg = synth.CONFIGS[4]
     ctx = hl.Context(local_rank, torch.cuda.current_stream())
+    if args.pipeline_only:
+        print(json.dumps(extra_config2_pipeline(torch, local_rank)), file=result_out, flush=True)
+        ctx.close()
+        return
     if args.head_sharded_only:
         res = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks)
         if rank == 0:
@@ -414,6 +466,7 @@ def main():
     if not args.no_extras:
         if world == 1:
             extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False))
+            extra["config2_backend_pipeline"] = extra_config2_pipeline(torch, local_rank)
         if cfg.n_head_kv % world == 0:
             extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
                                                                                peaks)

@@ -51,6 +51,7 @@ SYMBOLS = {
     "hl_b200_kv_append_seq": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _view_p, _i32, _i32, _vp, _i32]),
     "hl_b200_kv_append_batch": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _view_p, _i32, _vp, _vp, _i32]),
     "hl_b200_attn_prefill": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _i32, _vp, _i32, _view_p, _f32p]),
+    "hl_b200_attn_prefill_bcast": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _i32, _vp, _i32, _view_p, C.POINTER(_vp), _i32, _f32p]),
     "hl_b200_attn_decode": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p, _f32p]),
     "hl_b200_attn_decode_static": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p]),
     "hl_b200_prefill_host": (_i32, [_vp, _vp, _i32, _shape_p, _f32p, _f32p, _f32p, _i32, _i32, _vp, _i32, _f32p, _f32p]),

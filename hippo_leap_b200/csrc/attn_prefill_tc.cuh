@@ -33,6 +33,11 @@ struct PrefillTcArgs {
   const float2* cs_table;  // [n_pos][rope_dim/2] (cos, sin) of float(pos) * theta_i
   int32_t box_rows;        // rows per TMA box: 16, or 128 when a block holds whole 128-key tiles
   uint32_t oob_row;        // a row coordinate outside the pool: TMA fills such boxes with zeros
+  // Extra destinations of the output (same dtype and strides as p.out): peer GPUs' buffers mapped
+  // into this GPU's address space.  The epilogue stores every tile to all of them with plain stores
+  // over NVLink, so the all-gather of head outputs rides along with the compute.
+  void* bcast[7];
+  int32_t n_bcast;
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------
@@ -598,29 +603,34 @@ __global__ void __launch_bounds__(384, 1)
         tc_wait_ld();
         if (live) {
           const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(h) * a.out.hs + q4 * 32;
-          if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
-            __half* dst = static_cast<__half*>(const_cast<void*>(a.out.ptr)) + off;
-            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {  // destination 0 is the local output
+            void* obase = dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1];
+            if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
+              __half* dst = static_cast<__half*>(obase) + off;
+              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8)
-                *reinterpret_cast<uint4*>(dst + i) =
-                    make_uint4(pack_half2(oreg[i] * inv, oreg[i + 1] * inv), pack_half2(oreg[i + 2] * inv, oreg[i + 3] * inv),
-                               pack_half2(oreg[i + 4] * inv, oreg[i + 5] * inv), pack_half2(oreg[i + 6] * inv, oreg[i + 7] * inv));
+                for (int i = 0; i < 32; i += 8)
+                  *reinterpret_cast<uint4*>(dst + i) = make_uint4(
+                      pack_half2(oreg[i] * inv, oreg[i + 1] * inv), pack_half2(oreg[i + 2] * inv, oreg[i + 3] * inv),
+                      pack_half2(oreg[i + 4] * inv, oreg[i + 5] * inv), pack_half2(oreg[i + 6] * inv, oreg[i + 7] * inv));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                  *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+              }
+            } else if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F32 &&
+                       (reinterpret_cast<uintptr_t>(static_cast<float*>(obase) + off) & 15) == 0) {
+              float* dst = static_cast<float*>(obase) + off;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(dst + i) =
+                    make_float4(oreg[i] * inv, oreg[i + 1] * inv, oreg[i + 2] * inv, oreg[i + 3] * inv);
             } else {
+              View ov = a.out;
+              ov.ptr = obase;
 #pragma unroll
-              for (int i = 0; i < 32; i += 2)
-                *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+              for (int i = 0; i < 32; ++i) view_store(ov, trow, h, q4 * 32 + i, oreg[i] * inv);
             }
-          } else if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F32 &&
-                     (reinterpret_cast<uintptr_t>(static_cast<const float*>(a.out.ptr) + off) & 15) == 0) {
-            float* dst = static_cast<float*>(const_cast<void*>(a.out.ptr)) + off;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + i) =
-                  make_float4(oreg[i] * inv, oreg[i + 1] * inv, oreg[i + 2] * inv, oreg[i + 3] * inv);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) view_store(a.out, trow, h, q4 * 32 + i, oreg[i] * inv);
           }
         }
       }
@@ -658,7 +668,8 @@ inline bool hl_prefill_tc_default(const hl::PrefillArgs& a, int head_dim) {
 }
 
 template <int HD>
-static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a) {
+static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a,
+                                      void* const* bcast, int n_bcast) {
   using namespace hl;
   using Cfg = PrefillTcCfg<HD>;
   auto kern = attn_prefill_tc_kernel<HD>;
@@ -673,6 +684,8 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
   PrefillTcArgs ta{};
   ta.p = a;
   ta.cs_table = nullptr;
+  ta.n_bcast = n_bcast;
+  for (int i = 0; i < n_bcast; ++i) ta.bcast[i] = bcast[i];
   if (a.rope_dim == HD) {
     if (ctx->cs_len < n_pos || ctx->cs_half != half) {
       HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -702,6 +715,8 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
   return HL_OK;
 }
 
-inline int32_t hl_launch_prefill_tc(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a, int head_dim) {
-  return head_dim == 64 ? hl_launch_prefill_tc_t<64>(ctx, kv, layer, a) : hl_launch_prefill_tc_t<128>(ctx, kv, layer, a);
+inline int32_t hl_launch_prefill_tc(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a, int head_dim,
+                                    void* const* bcast = nullptr, int n_bcast = 0) {
+  return head_dim == 64 ? hl_launch_prefill_tc_t<64>(ctx, kv, layer, a, bcast, n_bcast)
+                        : hl_launch_prefill_tc_t<128>(ctx, kv, layer, a, bcast, n_bcast);
 }

@@ -545,9 +545,9 @@ static int32_t launch_prefill_mma(hl_ctx* ctx, hl_kv* kv, int32_t layer, const P
   return HL_OK;
 }
 
-extern "C" int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
-                                        const hl_view* q, int32_t n_tok, int32_t start_pos, const int32_t* block_table,
-                                        int32_t n_blocks_in_table, const hl_view* out, float* gpu_ms) {
+static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* q,
+                            int32_t n_tok, int32_t start_pos, const int32_t* block_table, int32_t n_blocks_in_table,
+                            const hl_view* out, void* const* bcast, int32_t n_bcast, float* gpu_ms) {
   int32_t rc = check_shape(ctx, kv, s, layer);
   if (rc == HL_OK) rc = check_view(ctx, q, "q");
   if (rc == HL_OK) rc = check_view(ctx, out, "out");
@@ -583,14 +583,35 @@ extern "C" int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, c
 
   rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
-  const bool want_tc = ctx->prefill_kernel == 2 || (ctx->prefill_kernel == 0 && hl_prefill_tc_default(a, s->head_dim));
+  const bool want_tc =
+      n_bcast > 0 || ctx->prefill_kernel == 2 || (ctx->prefill_kernel == 0 && hl_prefill_tc_default(a, s->head_dim));
   if (want_tc) {
     if (!hl_prefill_tc_supported(a, s->head_dim))
       return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: the tcgen05 kernel does not take this shape");
-    rc = hl_launch_prefill_tc(ctx, kv, layer, a, s->head_dim);
+    rc = hl_launch_prefill_tc(ctx, kv, layer, a, s->head_dim, bcast, n_bcast);
   } else {
     rc = s->head_dim == 64 ? launch_prefill_mma<64>(ctx, kv, layer, a) : launch_prefill_mma<128>(ctx, kv, layer, a);
   }
   if (rc != HL_OK) return rc;
   return hl_end_timing(ctx, gpu_ms);
+}
+
+extern "C" int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                        const hl_view* q, int32_t n_tok, int32_t start_pos, const int32_t* block_table,
+                                        int32_t n_blocks_in_table, const hl_view* out, float* gpu_ms) {
+  return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, nullptr, 0, gpu_ms);
+}
+
+extern "C" int32_t hl_b200_attn_prefill_bcast(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                              const hl_view* q, int32_t n_tok, int32_t start_pos,
+                                              const int32_t* block_table, int32_t n_blocks_in_table,
+                                              const hl_view* out, void* const* peer_out_ptrs, int32_t n_peers,
+                                              float* gpu_ms) {
+  if (!ctx) return HL_ERR_ARG;
+  if (n_peers < 0 || n_peers > 7) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: n_peers %d outside [0, 7]", n_peers);
+  if (n_peers > 0 && !peer_out_ptrs) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: null peer pointer list");
+  for (int i = 0; i < n_peers; ++i)
+    if (!peer_out_ptrs[i]) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: null peer pointer %d", i);
+  return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, peer_out_ptrs,
+                      n_peers, gpu_ms);
 }

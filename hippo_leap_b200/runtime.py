@@ -252,3 +252,16 @@ class Context:
     def selftest_wait_timeout(self, max_polls: int = 1000):
         """Launch the bounded-wait self-test; read the outcome with ``device_status()``."""
         self._check(self.lib.hl_b200_selftest_wait_timeout(self.handle, max_polls))
+
+    def attn_prefill_bcast(self, kv: KvPool, layer: int, shape: AttnShape, q, start_pos: int,
+                           block_table: torch.Tensor, out: torch.Tensor, peer_ptrs, timed: bool = False):
+        """hl_b200_attn_prefill_bcast: prefill whose epilogue also stores each tile to ``peer_ptrs``
+        (device addresses of the same output slice on other GPUs)."""
+        sc, qc, oc = shape.c(), view_of(q), view_of(out)
+        arr = (C.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_attn_prefill_bcast(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], start_pos,
+            _i32_dev(block_table), block_table.numel(), C.byref(oc), arr, len(peer_ptrs),
+            C.byref(ms) if timed else None))
+        return (out, ms.value) if timed else out

@@ -116,3 +116,40 @@ class HeadShardedPrefill:
                 self.full[c].copy_(self.local[c])
         main.wait_stream(self.comm_stream)
         return self.full
+
+
+class FusedHeadShardedPrefill:
+    """Head-sharded causal prefill with the all-gather of head outputs fused INTO the attention kernel.
+
+    Every rank allocates the full ``[n_head][n_tok][head_dim]`` fp16 result in symmetric memory (the same
+    buffer on every GPU, each mapped into the others' address spaces).  A rank's prefill kernel stores
+    each finished output tile of its own heads into its slice of the buffer on ALL ranks -- plain
+    stores to peer memory over NVLink, spread over the whole run of the kernel -- so when the kernels
+    end the gather is already done; only a barrier remains.  No collective kernel is launched.
+    """
+
+    def __init__(self, ctx, kv, shape, n_tok: int, n_head_total: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.ctx, self.kv, self.shape, self.n_tok = ctx, kv, shape, n_tok
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        hd = shape.head_dim
+        if self.world > 1:
+            self.full = symm.empty((n_head_total, n_tok, hd), dtype=torch.float16, device=device)
+            self.hdl = symm.rendezvous(self.full, group if group is not None else dist.group.WORLD)
+            ptrs = list(self.hdl.buffer_ptrs)
+        else:
+            self.full = torch.empty((n_head_total, n_tok, hd), dtype=torch.float16, device=device)
+            self.hdl, ptrs = None, [self.full.data_ptr()]
+        q_lo = self.rank * shape.n_head
+        self.local = self.full[q_lo:q_lo + shape.n_head]           # [n_head_local, n_tok, hd]
+        byte_off = q_lo * n_tok * hd * 2
+        self.peer_ptrs = [ptrs[p] + byte_off for p in range(self.world) if p != self.rank]
+
+    def run(self, q: torch.Tensor, block_table: torch.Tensor, layer: int = 0) -> torch.Tensor:
+        self.ctx.attn_prefill_bcast(self.kv, layer, self.shape, q, 0, block_table, self.local.permute(1, 0, 2),
+                                    self.peer_ptrs)
+        if self.hdl is not None:
+            self.hdl.barrier()  # every rank's kernel has finished: all slices of `full` are in place
+        return self.full

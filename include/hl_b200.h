@@ -145,6 +145,20 @@ int32_t hl_b200_attn_prefill(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_att
                              const int32_t* block_table, int32_t n_blocks_in_table,
                              const hl_view* out, float* gpu_ms);
 
+/* No counterpart in the reference (which has no multi-GPU code).  hl_b200_attn_prefill whose kernel
+ * ALSO stores every output tile to up to 7 more destinations with the layout of `out`: the same
+ * buffer on peer GPUs, mapped into this GPU's address space (CUDA IPC / symmetric memory).  With KV
+ * heads sharded across GPUs, each GPU passes as `out` its own head slice of the full
+ * [n_head][n_tok][head_dim] buffer and as peers the same slice of every other GPU's buffer: the
+ * all-gather of head outputs then happens inside the attention kernel, tile by tile over NVLink,
+ * instead of as a collective after it.  Peers must be synchronised by the caller before they read
+ * (a barrier after the call's stream work has completed on every rank). */
+int32_t hl_b200_attn_prefill_bcast(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                   const hl_view* q, int32_t n_tok, int32_t start_pos,
+                                   const int32_t* block_table, int32_t n_blocks_in_table,
+                                   const hl_view* out, void* const* peer_out_ptrs, int32_t n_peers,
+                                   float* gpu_ms);
+
 /* Replaces gpuQkNorm(Q) + the Q half of gpuRopeQKDecode + gpuAttentionDecode
  * (naive.nim:4697-4717): one query token per sequence, sequence i attending its first
  * ctx_lens[i] cached keys (the new token's own K/V included: curLen = pos + 1).

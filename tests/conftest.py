@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100) GPU; run with -m gpu")
+    config.addinivalue_line("markers", "expects_device_status: the test provokes and reads the device status word itself")
 
 
 @pytest.fixture(scope="session")

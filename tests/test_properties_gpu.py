@@ -233,3 +233,31 @@ def test_head_sharded_prefill_runner_single_rank_equals_plain_prefill(hl_ctx):
     assert_parity(got[[5, 700, 2047], [0, 9, 31]].cpu().numpy(), want, "head-sharded runner rows",
                   max_abs_tol=4e-3, rel_l2_tol=2e-3)  # fp16 OUTPUT variant: its own rounding on top of the path's
     kv.destroy()
+
+
+def test_prefill_bcast_writes_identical_copies_to_every_destination(hl_ctx):
+    """The fused gather path on one GPU: three extra destinations (local buffers standing in for peers'
+    mapped memory) must receive bit-identical copies of the output, for both output dtypes."""
+    cfg = synth.CONFIGS[3]
+    S, bt = 700, 16
+    q, k, v = synth.gen_qkv(cfg, S)
+    qw, kw = synth.gen_norm_weights(cfg)
+    hl_ctx.set_rope(cfg.theta())
+    shape = _shape_for(cfg, hl.HL_ROPE_SPLIT_HALF, qw, kw)
+    tq, tk, tv = _upload(q, k, v)
+    nb = (S + bt - 1) // bt
+    tt = torch.randperm(nb, device="cuda").to(torch.int32)
+    kv = hl_ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, nb)
+    hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
+    want = hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt)
+    for dtype in (torch.float16, torch.float32):
+        bufs = [torch.zeros((cfg.n_head, S, cfg.head_dim), dtype=dtype, device="cuda") for _ in range(4)]
+        hl_ctx.attn_prefill_bcast(kv, 0, shape, tq, 0, tt, bufs[0].permute(1, 0, 2), [b.data_ptr() for b in bufs[1:]])
+        torch.cuda.synchronize()
+        for b in bufs[1:]:
+            assert torch.equal(b, bufs[0])
+        tol = 4e-3 if dtype == torch.float16 else 3e-4  # tcgen05 path vs the default path, plus fp16 rounding
+        assert float((bufs[0].permute(1, 0, 2).float() - want).abs().max()) < tol
+    with pytest.raises(hl.HlError):
+        hl_ctx.attn_prefill_bcast(kv, 0, shape, tq, 0, tt, bufs[0].permute(1, 0, 2), [1] * 8)
+    kv.destroy()
