@@ -22,6 +22,7 @@ namespace hl {
 
 struct DecodeArgs {
   View q, out;
+  View gate;  // optional sigmoid gate on the output, same indexing as out; ptr == nullptr: none
   const float* q_norm_w;
   const float* theta;
   const int32_t* ctx_lens;
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     }
     const int h = kvh * a.group + r;
     if (n_chunks_seq == 1) {
-      view_store(a.out, b, h, d, acc / L);
+      view_store(a.out, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
     } else {
       const int64_t pi = (static_cast<int64_t>(b) * a.n_head + h) * a.max_chunks + chunk;
       a.part_o[pi * HD + d] = acc;
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
     L += a.part_ml[(p0 + ci) * 2 + 1] * f;
     acc += a.part_o[(p0 + ci) * HD + d] * f;
   }
-  view_store(a.out, b, h, d, acc / L);
+  view_store(a.out, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
 }
 
 }  // namespace hl

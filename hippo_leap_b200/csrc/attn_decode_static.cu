@@ -129,6 +129,7 @@ extern "C" int32_t hl_b200_attn_decode_static(hl_ctx* ctx, hl_kv* kv, int32_t la
                    batch, s->n_head, a.max_chunks, need, kStaticTriples);
   a.q = hl::View{q->ptr, q->dtype, q->tok_stride, q->head_stride, q->dim_stride};
   a.out = hl::View{out->ptr, out->dtype, out->tok_stride, out->head_stride, out->dim_stride};
+  a.gate = hl::View{nullptr, 0, 0, 0, 0};
   a.q_norm_w = s->q_norm_w;
   a.theta = ctx->theta_d;
   a.ctx_lens = ctx_lens;

@@ -19,6 +19,7 @@ namespace hl {
 
 struct PrefillArgs {
   View q, out;
+  View gate;  // optional sigmoid gate on the output, same indexing as out; ptr == nullptr: none
   const float* q_norm_w;
   const float* theta;
   const int32_t* block_table;
@@ -271,12 +272,12 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   for (int nt = 0; nt < HD / 8; ++nt) {
     const int d = nt * 8 + 2 * tq;
     if (tr0 < a.n_tok) {
-      view_store(a.out, tr0, h, d, o[nt][0] * inv0);
-      view_store(a.out, tr0, h, d + 1, o[nt][1] * inv0);
+      view_store(a.out, tr0, h, d, apply_gate(a.gate, tr0, h, d, o[nt][0] * inv0));
+      view_store(a.out, tr0, h, d + 1, apply_gate(a.gate, tr0, h, d + 1, o[nt][1] * inv0));
     }
     if (tr1 < a.n_tok) {
-      view_store(a.out, tr1, h, d, o[nt][2] * inv1);
-      view_store(a.out, tr1, h, d + 1, o[nt][3] * inv1);
+      view_store(a.out, tr1, h, d, apply_gate(a.gate, tr1, h, d, o[nt][2] * inv1));
+      view_store(a.out, tr1, h, d + 1, apply_gate(a.gate, tr1, h, d + 1, o[nt][3] * inv1));
     }
   }
 }

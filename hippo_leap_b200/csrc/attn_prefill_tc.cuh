@@ -602,6 +602,12 @@ __global__ void __launch_bounds__(384, 1)
         tc_ld32f(tO + q4 * 32, oreg);
         tc_wait_ld();
         if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oreg[i] *= inv;
+          if (a.gate.ptr != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] = apply_gate(a.gate, trow, h, q4 * 32 + i, oreg[i]);
+          }
           const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(h) * a.out.hs + q4 * 32;
           for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {  // destination 0 is the local output
             void* obase = dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1];
@@ -611,12 +617,12 @@ __global__ void __launch_bounds__(384, 1)
 #pragma unroll
                 for (int i = 0; i < 32; i += 8)
                   *reinterpret_cast<uint4*>(dst + i) = make_uint4(
-                      pack_half2(oreg[i] * inv, oreg[i + 1] * inv), pack_half2(oreg[i + 2] * inv, oreg[i + 3] * inv),
-                      pack_half2(oreg[i + 4] * inv, oreg[i + 5] * inv), pack_half2(oreg[i + 6] * inv, oreg[i + 7] * inv));
+                      pack_half2(oreg[i], oreg[i + 1]), pack_half2(oreg[i + 2], oreg[i + 3]),
+                      pack_half2(oreg[i + 4], oreg[i + 5]), pack_half2(oreg[i + 6], oreg[i + 7]));
               } else {
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)
-                  *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i] * inv, oreg[i + 1] * inv);
+                  *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i], oreg[i + 1]);
               }
             } else if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F32 &&
                        (reinterpret_cast<uintptr_t>(static_cast<float*>(obase) + off) & 15) == 0) {
@@ -624,12 +630,12 @@ __global__ void __launch_bounds__(384, 1)
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
                 *reinterpret_cast<float4*>(dst + i) =
-                    make_float4(oreg[i] * inv, oreg[i + 1] * inv, oreg[i + 2] * inv, oreg[i + 3] * inv);
+                    make_float4(oreg[i], oreg[i + 1], oreg[i + 2], oreg[i + 3]);
             } else {
               View ov = a.out;
               ov.ptr = obase;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) view_store(ov, trow, h, q4 * 32 + i, oreg[i] * inv);
+              for (int i = 0; i < 32; ++i) view_store(ov, trow, h, q4 * 32 + i, oreg[i]);
             }
           }
         }

@@ -463,13 +463,13 @@ int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_
   return static_cast<int32_t>(chunk);
 }
 
-extern "C" int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
-                                       const hl_view* q, int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h,
-                                       const int32_t* block_tables, int32_t max_blocks_per_seq, const hl_view* out,
-                                       float* gpu_ms) {
+static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* q,
+                           int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h, const int32_t* block_tables,
+                           int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out, float* gpu_ms) {
   int32_t rc = check_shape(ctx, kv, s, layer);
   if (rc == HL_OK) rc = check_view(ctx, q, "q");
   if (rc == HL_OK) rc = check_view(ctx, out, "out");
+  if (rc == HL_OK && gate) rc = check_view(ctx, gate, "gate");
   if (rc != HL_OK) return rc;
   if (batch <= 0 || batch > 65535) return hl_fail(ctx, HL_ERR_ARG, "decode: batch %d outside [1, 65535]", batch);
   if (!ctx_lens || !block_tables || max_blocks_per_seq <= 0) return hl_fail(ctx, HL_ERR_ARG, "decode: null ctx_lens or block table");
@@ -500,6 +500,7 @@ extern "C" int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, co
   }
   a.q = to_view(q);
   a.out = to_view(out);
+  a.gate = gate ? to_view(gate) : View{nullptr, 0, 0, 0, 0};
   a.q_norm_w = s->q_norm_w;
   a.theta = ctx->theta_d;
   a.ctx_lens = ctx_lens;
@@ -525,6 +526,24 @@ extern "C" int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, co
   return hl_end_timing(ctx, gpu_ms);
 }
 
+extern "C" int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                       const hl_view* q, int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h,
+                                       const int32_t* block_tables, int32_t max_blocks_per_seq, const hl_view* out,
+                                       float* gpu_ms) {
+  return decode_impl(ctx, kv, layer, s, q, batch, ctx_lens, max_ctx_h, block_tables, max_blocks_per_seq, nullptr, out,
+                     gpu_ms);
+}
+
+extern "C" int32_t hl_b200_attn_decode_gated(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                             const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                                             int32_t max_ctx_h, const int32_t* block_tables,
+                                             int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out,
+                                             float* gpu_ms) {
+  if (ctx && !gate) return hl_fail(ctx, HL_ERR_ARG, "decode_gated: null gate view");
+  return decode_impl(ctx, kv, layer, s, q, batch, ctx_lens, max_ctx_h, block_tables, max_blocks_per_seq, gate, out,
+                     gpu_ms);
+}
+
 // ---------------------------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------------------------
@@ -547,10 +566,12 @@ static int32_t launch_prefill_mma(hl_ctx* ctx, hl_kv* kv, int32_t layer, const P
 
 static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* q,
                             int32_t n_tok, int32_t start_pos, const int32_t* block_table, int32_t n_blocks_in_table,
-                            const hl_view* out, void* const* bcast, int32_t n_bcast, float* gpu_ms) {
+                            const hl_view* out, void* const* bcast, int32_t n_bcast, float* gpu_ms,
+                            const hl_view* gate = nullptr) {
   int32_t rc = check_shape(ctx, kv, s, layer);
   if (rc == HL_OK) rc = check_view(ctx, q, "q");
   if (rc == HL_OK) rc = check_view(ctx, out, "out");
+  if (rc == HL_OK && gate) rc = check_view(ctx, gate, "gate");
   if (rc != HL_OK) return rc;
   if (n_tok <= 0) return hl_fail(ctx, HL_ERR_ARG, "prefill requires at least one token");
   if (start_pos < 0) return hl_fail(ctx, HL_ERR_ARG, "prefill: negative start_pos");
@@ -564,6 +585,7 @@ static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
   PrefillArgs a{};
   a.q = to_view(q);
   a.out = to_view(out);
+  a.gate = gate ? to_view(gate) : View{nullptr, 0, 0, 0, 0};
   a.q_norm_w = s->q_norm_w;
   a.theta = ctx->theta_d;
   a.block_table = block_table;
@@ -614,4 +636,13 @@ extern "C" int32_t hl_b200_attn_prefill_bcast(hl_ctx* ctx, hl_kv* kv, int32_t la
     if (!peer_out_ptrs[i]) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: null peer pointer %d", i);
   return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, peer_out_ptrs,
                       n_peers, gpu_ms);
+}
+
+extern "C" int32_t hl_b200_attn_prefill_gated(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                              const hl_view* q, int32_t n_tok, int32_t start_pos,
+                                              const int32_t* block_table, int32_t n_blocks_in_table,
+                                              const hl_view* gate, const hl_view* out, float* gpu_ms) {
+  if (ctx && !gate) return hl_fail(ctx, HL_ERR_ARG, "prefill_gated: null gate view");
+  return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, nullptr, 0, gpu_ms,
+                      gate);
 }

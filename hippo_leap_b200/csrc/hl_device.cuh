@@ -142,6 +142,14 @@ __device__ __forceinline__ void view_store(const View& v, int64_t t, int64_t h, 
     static_cast<float*>(const_cast<void*>(v.ptr))[off] = x;
 }
 
+// Optional output gate of the attention output: x * sigmoid(g), sigmoid(g) = 1 / (1 + expf(-g)), as
+// attnGateKernel (src/hippo_leap/backends/naive.nim:2287-2293).  gate.ptr == nullptr means no gate.
+__device__ __forceinline__ float apply_gate(const View& gate, int64_t t, int64_t h, int64_t d, float x) {
+  if (gate.ptr == nullptr) return x;
+  const float g = view_load(gate, t, h, d);
+  return (1.0f / (1.0f + expf(-g))) * x;
+}
+
 // ---- row prologue: (RMSNorm) -> RoPE -------------------------------------------------------
 // One WARP transforms one head row x[0..HD) held in shared memory as float32, in place.
 //   norm : x <- x * (1/sqrt(mean(x^2) + eps)) * w        (naive.nim:2906-2917; tensor.nim:92-100)

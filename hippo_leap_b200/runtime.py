@@ -180,30 +180,45 @@ class Context:
     # -- attention ---------------------------------------------------------------------------
     def attn_prefill(self, kv: KvPool, layer: int, shape: AttnShape, q, start_pos: int,
                      block_table: torch.Tensor, out: torch.Tensor | None = None,
-                     timed: bool = False):
+                     timed: bool = False, gate: torch.Tensor | None = None):
+        """``gate`` ([n_tok, n_head, hd] view): out <- sigmoid(gate) * out in the kernel epilogue."""
         if out is None:
             out = torch.empty((q.shape[0], shape.n_head, shape.head_dim), dtype=torch.float32,
                               device=q.device)
         sc, qc, oc = shape.c(), view_of(q), view_of(out)
         ms = C.c_float(0.0)
-        self._check(self.lib.hl_b200_attn_prefill(
-            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], start_pos,
-            _i32_dev(block_table), block_table.numel(), C.byref(oc),
-            C.byref(ms) if timed else None))
+        if gate is None:
+            self._check(self.lib.hl_b200_attn_prefill(
+                self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], start_pos,
+                _i32_dev(block_table), block_table.numel(), C.byref(oc),
+                C.byref(ms) if timed else None))
+        else:
+            gc = view_of(gate)
+            self._check(self.lib.hl_b200_attn_prefill_gated(
+                self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], start_pos,
+                _i32_dev(block_table), block_table.numel(), C.byref(gc), C.byref(oc),
+                C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
 
     def attn_decode(self, kv: KvPool, layer: int, shape: AttnShape, q, ctx_lens: torch.Tensor,
                     max_ctx: int, block_tables: torch.Tensor, out: torch.Tensor | None = None,
-                    timed: bool = False):
+                    timed: bool = False, gate: torch.Tensor | None = None):
         if out is None:
             out = torch.empty((q.shape[0], shape.n_head, shape.head_dim), dtype=torch.float32,
                               device=q.device)
         sc, qc, oc = shape.c(), view_of(q), view_of(out)
         ms = C.c_float(0.0)
-        self._check(self.lib.hl_b200_attn_decode(
-            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0],
-            _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
-            C.byref(oc), C.byref(ms) if timed else None))
+        if gate is None:
+            self._check(self.lib.hl_b200_attn_decode(
+                self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0],
+                _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
+                C.byref(oc), C.byref(ms) if timed else None))
+        else:
+            gc = view_of(gate)
+            self._check(self.lib.hl_b200_attn_decode_gated(
+                self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0],
+                _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
+                C.byref(gc), C.byref(oc), C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
 
     # -- host-buffer forms (inputs and result in host memory; the call synchronises) ------------

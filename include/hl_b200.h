@@ -170,6 +170,22 @@ int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
                             int32_t max_ctx_h, const int32_t* block_tables,
                             int32_t max_blocks_per_seq, const hl_view* out, float* gpu_ms);
 
+/* The two attention calls with the output gate of the qwen3.5-MoE attention layers fused into
+ * their epilogue: out <- sigmoid(gate) * out, replacing gpuAttnGate (naive.nim:2287-2300, applied at
+ * naive.nim:4259-4260).  `gate` is indexed like `out` ([n_tok][n_head][head_dim] view).  The reference
+ * de-interleaves a fused Q|gate projection first (gpuDeinterleaveQGatePrefill, naive.nim:2427-2456);
+ * with strided views that copy is unnecessary: q = {ptr, head_stride 2*head_dim*S, ...} and
+ * gate = {ptr + head_dim*S, same strides} address the fused buffer directly. */
+int32_t hl_b200_attn_prefill_gated(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                   const hl_view* q, int32_t n_tok, int32_t start_pos,
+                                   const int32_t* block_table, int32_t n_blocks_in_table,
+                                   const hl_view* gate, const hl_view* out, float* gpu_ms);
+int32_t hl_b200_attn_decode_gated(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                  const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                                  int32_t max_ctx_h, const int32_t* block_tables,
+                                  int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out,
+                                  float* gpu_ms);
+
 /* No counterpart in the reference.  hl_b200_attn_decode without any allocation, for callers that have
  * given all device memory to their own pool or cannot take the device-wide synchronisation of
  * cudaMalloc / cudaFree inside the decode loop.  Same arguments and result as hl_b200_attn_decode

@@ -51,6 +51,7 @@ def lib() -> C.CDLL:
             fp, C.c_int, fp, fp, C.c_float, C.c_int, C.POINTER(C.c_int32), C.c_long, fp, fp,
             C.c_int]
         L.hl_ref_attn_forward.restype = C.c_int
+        L.hl_ref_attn_gate.argtypes = [fp, fp, C.c_long]
         L.hl_ref_max_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -154,6 +155,15 @@ def attn_forward(q, k, v, cache: SeqCache, *, theta, rope_mode: int, rope_dim: i
         raise ValueError(f"hl_ref_attn_forward rejected its arguments (rc={rc})")
     cache.cur_len += T
     return (out, q_rot) if return_q_rot else out
+
+
+def attn_gate(out, gate) -> np.ndarray:
+    """sigmoid(gate) * out, elementwise float32 (naive.nim:2287-2293)."""
+    o = _f32(out).copy()
+    g = _f32(gate)
+    assert o.shape == g.shape
+    lib().hl_ref_attn_gate(_p(o), _p(g), o.size)
+    return o
 
 
 def max_threads() -> int:

@@ -25,6 +25,7 @@
  *   kvh = h div (nHead div nHeadKv)             backends/naive.nim:3307-3308
  *   score = dot * (1/sqrt(headDim)) after the sum   backends/naive.nim:3328, 3415
  *   causal: query at position p attends keys 0..p   backends/naive.nim:3402
+ *   optional sigmoid output gate                    backends/naive.nim:2287-2293
  * Attention rows are composed ONLY from the part-1 primitives (matmul for q.K^T and P.V,
  * softmax_last_dim for the row), so that every float32 rounding happens where tensor.nim
  * would put it.
@@ -251,6 +252,16 @@ int hl_ref_attn_forward(const float* q, const float* k, const float* v, float* k
     }
   }
   return err;
+}
+
+/* Attention output gate of the qwen3.5-MoE layers: dst <- sigmoid(gate) * dst, float32, with
+ * sigmoid(g) = 1 / (1 + expf(-g)).  backends/naive.nim:2287-2293 (attnGateKernel), applied to the
+ * attention output before the output projection (naive.nim:4259-4260). */
+void hl_ref_attn_gate(float* dst, const float* gate, long n) {
+  for (long i = 0; i < n; ++i) {
+    const float sig = 1.0f / (1.0f + expf(-gate[i]));
+    dst[i] = sig * dst[i];
+  }
 }
 
 int hl_ref_max_threads(void) {
