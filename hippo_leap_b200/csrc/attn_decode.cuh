@@ -49,8 +49,8 @@ struct DecodeCfg {
   static constexpr int kMergeBytes = NW * 16 * HD * 4 + NW * 16 * 8;
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static_assert(kRingBytes >= kMergeBytes, "merge buffer reuses the ring");
-  static_assert(kRingBytes >= 16 * HD * 4, "fp32 Q staging reuses the ring");
-  static constexpr int kSmemBytes = 1024 /*align slack*/ + kQBytes + kRingBytes + 2 * STAGES * 8;
+  static constexpr int kQStageBytes = 16 * HD * 4;  // fp32 staging of the query rows (own area: the ring fills meanwhile)
+  static constexpr int kSmemBytes = 1024 /*align slack*/ + kQBytes + kRingBytes + kQStageBytes + 2 * STAGES * 8;
   static constexpr int kThreads = (NW + 1) * 32;
 };
 
@@ -73,7 +73,8 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   const uint32_t q_tile = base;
   const uint32_t ring = base + Cfg::kQBytes;
   uint8_t* ring_gen = gen + Cfg::kQBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(ring_gen + Cfg::kRingBytes);
+  float* q_stage = reinterpret_cast<float*>(ring_gen + Cfg::kRingBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring_gen + Cfg::kRingBytes + Cfg::kQStageBytes);
   uint64_t* empty = full + STAGES;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -86,24 +87,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     mbar_fence_init();
   }
 
-  // ---- Q prologue: G rows -> norm -> RoPE at pos = ctx-1 -> fp16 swizzled tile (rows >= G zero)
-  {
-    float* qf = reinterpret_cast<float*>(ring_gen);  // [16][HD] fp32 staging (ring not yet in use)
-    const int pos = ctx - 1;
-    for (int r = warp; r < 16; r += NW + 1) {
-      float* x = qf + r * HD;
-      const bool live = r < a.group;
-      if (live) {
-        const int h = kvh * a.group + r;
-#pragma unroll
-        for (int d = lane; d < HD; d += 32) x[d] = view_load(a.q, b, h, d);
-        __syncwarp();
-        norm_rope_row<HD>(x, a.q_norm_w, a.eps, a.theta, a.rope_dim, a.rope_mode, pos, lane);
-      }
-      store_row_fp16_swz<HD>(q_tile, Cfg::kQHalfBytes, r, x, lane, !live);
-    }
-  }
-  __syncthreads();  // Q tile + barriers visible; ring free for TMA
+  __syncthreads();  // barriers initialised: the producer may start filling the ring at once
 
   if (warp == NW) {
     // ================= producer warp =================
@@ -147,6 +131,24 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   }
 
   // ================= consumer warps =================
+  // ---- Q prologue (while the first K/V stages are in flight): G rows -> norm -> RoPE at pos = ctx-1
+  //      -> fp16 swizzled tile (rows >= G zero)
+  {
+    const int pos = ctx - 1;
+    for (int r = warp; r < 16; r += NW) {
+      float* x = q_stage + r * HD;
+      const bool live = r < a.group;
+      if (live) {
+        const int h = kvh * a.group + r;
+#pragma unroll
+        for (int d = lane; d < HD; d += 32) x[d] = view_load(a.q, b, h, d);
+        __syncwarp();
+        norm_rope_row<HD>(x, a.q_norm_w, a.eps, a.theta, a.rope_dim, a.rope_mode, pos, lane);
+      }
+      store_row_fp16_swz<HD>(q_tile, Cfg::kQHalfBytes, r, x, lane, !live);
+    }
+  }
+  named_bar_sync(2, NW * 32);  // the whole Q tile is written before any warp reads its fragments
   const int g = lane >> 2, tq = lane & 3;
   uint32_t qa[HD / 16][4];
   {
