@@ -355,6 +355,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--prefill-kernel", type=int, default=0, help="0 auto, 1 warp-MMA, 2 tcgen05, 3 tcgen05 on SM pairs")
     ap.add_argument("--pipeline-only", action="store_true", help="measure only the config 2 backend pipeline")
     ap.add_argument("--head-sharded-only", action="store_true",
                     help="measure only the head-sharded config 5 prefill + all-gather at N GPUs")
@@ -402,7 +403,7 @@ def main():
         print(json.dumps(res), file=result_out, flush=True)
         ctx.close()
         return
-    ctx.set_tuning(args.decode_chunk, 0)
+    ctx.set_tuning(args.decode_chunk, args.prefill_kernel)
     w = setup_decode(ctx, cfg, rank, device)
     B = len(w["ctx_lens"])
 

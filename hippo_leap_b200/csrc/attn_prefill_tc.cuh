@@ -673,26 +673,19 @@ inline bool hl_prefill_tc_default(const hl::PrefillArgs& a, int head_dim) {
   return hl_prefill_tc_supported(a, head_dim) && a.n_tok >= 256;
 }
 
-template <int HD>
-static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a,
-                                      void* const* bcast, int n_bcast) {
+// Fills the kernel arguments shared by the tcgen05 prefill kernels: the cos/sin table up to the last position
+// of this call (grow-only, rebuilt when theta changes), the out-of-bounds row, the broadcast destinations.
+static int32_t hl_prefill_tc_fill_args(hl_ctx* ctx, hl_kv* kv, const hl::PrefillArgs& a, int head_dim,
+                                       void* const* bcast, int n_bcast, hl::PrefillTcArgs* out) {
   using namespace hl;
-  using Cfg = PrefillTcCfg<HD>;
-  auto kern = attn_prefill_tc_kernel<HD>;
-  static bool configured[16] = {};
-  if (!configured[ctx->device & 15]) {
-    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    configured[ctx->device & 15] = true;
-  }
-  // cos/sin table up to the last position of this call (grow-only, rebuilt when theta changes)
   const int n_pos = a.start_pos + a.n_tok;
   const int half = a.rope_dim / 2;
-  PrefillTcArgs ta{};
+  PrefillTcArgs& ta = *out;
   ta.p = a;
   ta.cs_table = nullptr;
   ta.n_bcast = n_bcast;
   for (int i = 0; i < n_bcast; ++i) ta.bcast[i] = bcast[i];
-  if (a.rope_dim == HD) {
+  if (a.rope_dim == head_dim) {
     if (ctx->cs_len < n_pos || ctx->cs_half != half) {
       HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       if (ctx->cs_table) cudaFree(ctx->cs_table);
@@ -710,9 +703,27 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
     }
     ta.cs_table = static_cast<const float2*>(ctx->cs_table);
   }
+  ta.box_rows = 16;
+  ta.oob_row = static_cast<uint32_t>(static_cast<uint64_t>(kv->num_blocks) * kv->n_head_kv * kv->block_tokens);
+  return HL_OK;
+}
+
+template <int HD>
+static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl::PrefillArgs& a,
+                                      void* const* bcast, int n_bcast) {
+  using namespace hl;
+  using Cfg = PrefillTcCfg<HD>;
+  auto kern = attn_prefill_tc_kernel<HD>;
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[ctx->device & 15] = true;
+  }
+  PrefillTcArgs ta{};
+  int32_t rc = hl_prefill_tc_fill_args(ctx, kv, a, HD, bcast, n_bcast, &ta);
+  if (rc != HL_OK) return rc;
   const bool wide = kv->block_tokens % 128 == 0;
   ta.box_rows = wide ? 128 : 16;
-  ta.oob_row = static_cast<uint32_t>(static_cast<uint64_t>(kv->num_blocks) * kv->n_head_kv * kv->block_tokens);
   dim3 grid((a.n_tok + 255) / 256, a.n_head);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(wide ? kv->k_map128[layer] : kv->k_map[layer],
                                                               wide ? kv->v_map128[layer] : kv->v_map[layer], ta);

@@ -16,6 +16,7 @@
 #include "attn_decode.cuh"
 #include "attn_prefill_mma.cuh"
 #include "attn_prefill_tc.cuh"
+#include "attn_prefill_tc2.cuh"
 #include "host_common.h"
 #include "kv_append.cuh"
 
@@ -196,7 +197,7 @@ extern "C" int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, 
   if (!ctx) return HL_ERR_ARG;
   if (decode_chunk_tokens < 0 || decode_chunk_tokens % 64 != 0)
     return hl_fail(ctx, HL_ERR_ARG, "decode_chunk_tokens must be 0 or a multiple of 64");
-  if (prefill_kernel < 0 || prefill_kernel > 2) return hl_fail(ctx, HL_ERR_ARG, "prefill_kernel must be 0, 1 or 2");
+  if (prefill_kernel < 0 || prefill_kernel > 3) return hl_fail(ctx, HL_ERR_ARG, "prefill_kernel must be 0..3");
   ctx->decode_chunk = decode_chunk_tokens;
   ctx->prefill_kernel = prefill_kernel;
   return HL_OK;
@@ -607,7 +608,11 @@ static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
   if (rc != HL_OK) return rc;
   const bool want_tc =
       n_bcast > 0 || ctx->prefill_kernel == 2 || (ctx->prefill_kernel == 0 && hl_prefill_tc_default(a, s->head_dim));
-  if (want_tc) {
+  if (ctx->prefill_kernel == 3) {
+    if (!hl_prefill_tc2_supported(a, s->head_dim))
+      return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: the two-SM tcgen05 kernel takes head_dim 128 only");
+    rc = hl_launch_prefill_tc2(ctx, kv, layer, a, bcast, n_bcast);
+  } else if (want_tc) {
     if (!hl_prefill_tc_supported(a, s->head_dim))
       return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: the tcgen05 kernel does not take this shape");
     rc = hl_launch_prefill_tc(ctx, kv, layer, a, s->head_dim, bcast, n_bcast);

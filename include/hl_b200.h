@@ -224,7 +224,7 @@ int32_t hl_b200_decode_step_host(hl_ctx* ctx, hl_kv* kv, int32_t layer,
 int32_t hl_b200_selftest_wait_timeout(hl_ctx* ctx, int32_t max_polls);
 
 /* Tunables (0 = automatic): tokens per split-KV chunk for decode; which prefill kernel
- * runs (0 auto, 1 = warp-MMA kernel, 2 = tcgen05 kernel). */
+ * runs (0 auto, 1 = warp-MMA kernel, 2 = tcgen05 kernel, 3 = tcgen05 kernel on SM pairs, head_dim 128). */
 int32_t hl_b200_set_tuning(hl_ctx* ctx, int32_t decode_chunk_tokens, int32_t prefill_kernel);
 
 #ifdef __cplusplus
