@@ -386,6 +386,7 @@ def main():
     peaks = load_peaks()
     cfg = synth.CONFIGS[4]
     ctx = hl.Context(local_rank, torch.cuda.current_stream())
+    ctx.set_tuning(args.decode_chunk, args.prefill_kernel)
     if args.pipeline_only:
         print(json.dumps(extra_config2_pipeline(torch, local_rank)), file=result_out, flush=True)
         ctx.close()
@@ -403,7 +404,6 @@ def main():
         print(json.dumps(res), file=result_out, flush=True)
         ctx.close()
         return
-    ctx.set_tuning(args.decode_chunk, args.prefill_kernel)
     w = setup_decode(ctx, cfg, rank, device)
     B = len(w["ctx_lens"])
 
