@@ -201,16 +201,19 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int b_mn_major) 
 
 template <int HD>
 struct PrefillTcCfg {
-  static constexpr int kStages = HD == 128 ? 2 : 4;
+  static constexpr int kStagesK = HD == 128 ? 3 : 4;  // K runs further ahead than V: Q K^T of block j+1 is issued
+  static constexpr int kStagesV = HD == 128 ? 2 : 4;  // one P V earlier than V of block j+1 is needed
   static constexpr int kHalves = HD / 64;
   static constexpr int kHalfBytes = 128 * 128;              // 128 rows x 64 halfs
   static constexpr int kTileBytes = kHalves * kHalfBytes;   // one Q tile, one K block or one V block
   static constexpr int kQOff = 0;
   static constexpr int kKOff = 2 * kTileBytes;
-  static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  static constexpr int kRowOff = kVOff + kStages * kTileBytes;  // fp32 row staging, 8 warps (slow prologue)
-  static constexpr int kBarOff = kRowOff + 8 * HD * 4;
-  static constexpr int kNumBars = 4 * kStages + 7;
+  static constexpr int kVOff = kKOff + kStagesK * kTileBytes;
+  // fp32 row staging of the general (slow) query prologue: 8 warps x one row.  It borrows the LAST V
+  // stage, which the producer does not fill before the prologue has finished in that mode.
+  static constexpr int kRowOff = kVOff + (kStagesV - 1) * kTileBytes;
+  static constexpr int kBarOff = kVOff + kStagesV * kTileBytes;
+  static constexpr int kNumBars = 2 * kStagesK + 2 * kStagesV + 7;
   static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 16;
   static constexpr int kThreads = 384;  // 12 warps: two softmax warpgroups + one warpgroup holding the TMA and MMA warps
   static constexpr int kTmemCols = 512;
@@ -234,8 +237,9 @@ __global__ void __launch_bounds__(384, 1)
     attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                            PrefillTcArgs ta) {
   using Cfg = PrefillTcCfg<HD>;
-  constexpr int S = Cfg::kStages;
+  constexpr int SK = Cfg::kStagesK, SV = Cfg::kStagesV;
   const PrefillArgs& a = ta.p;
+  const bool fast_prologue = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
   const int q_blk = gridDim.x - 1 - blockIdx.x;  // longest first
   const int h = blockIdx.y;
   const int kvh = h / a.group;
@@ -246,13 +250,13 @@ __global__ void __launch_bounds__(384, 1)
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen + Cfg::kBarOff);
   uint64_t* k_full = bars;
-  uint64_t* k_empty = bars + S;
-  uint64_t* v_full = bars + 2 * S;
-  uint64_t* v_empty = bars + 3 * S;
-  uint64_t* s_full = bars + 4 * S;      // [2]
-  uint64_t* p_full = bars + 4 * S + 2;  // [2]
-  uint64_t* o_full = bars + 4 * S + 4;  // [2]
-  uint64_t* q_ready = bars + 4 * S + 6;
+  uint64_t* k_empty = bars + SK;
+  uint64_t* v_full = bars + 2 * SK;
+  uint64_t* v_empty = bars + 2 * SK + SV;
+  uint64_t* s_full = bars + 2 * SK + 2 * SV;      // [2]
+  uint64_t* p_full = bars + 2 * SK + 2 * SV + 2;  // [2]
+  uint64_t* o_full = bars + 2 * SK + 2 * SV + 4;  // [2]
+  uint64_t* q_ready = bars + 2 * SK + 2 * SV + 6;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -270,9 +274,11 @@ __global__ void __launch_bounds__(384, 1)
   const int k_end_max = max(k_end[0], k_end[1]);
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
+    for (int s = 0; s < SK; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < SV; ++s) {
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
@@ -311,8 +317,7 @@ __global__ void __launch_bounds__(384, 1)
     const int n_boxes = boxes_per_half * Cfg::kHalves;      // per K (or V) block: <= 16
     const int box_bytes = ta.box_rows * 128;
     for (int j = 0; j < n_max; ++j) {
-      const int s = j % S;
-      const uint32_t par = ((j / S) - 1) & 1;
+      const int sk = j % SK, sv = j % SV;
       // this lane's box of the block: which row group, which column half
       const int grp = lane / Cfg::kHalves, hh = lane % Cfg::kHalves;
       int row = static_cast<int>(ta.oob_row);
@@ -330,17 +335,19 @@ __global__ void __launch_bounds__(384, 1)
       }
       const uint32_t dst_off = hh * Cfg::kHalfBytes + grp * box_bytes;
       // K block j
-      if (j >= S) tc_wait(&k_empty[s], par, a.status, 500 + s, abort_flag);
-      if (lane == 0) mbar_arrive_expect_tx(&k_full[s], Cfg::kTileBytes);
+      if (j >= SK) tc_wait(&k_empty[sk], ((j / SK) - 1) & 1, a.status, 500 + sk, abort_flag);
+      if (lane == 0) mbar_arrive_expect_tx(&k_full[sk], Cfg::kTileBytes);
       __syncwarp();
       if (lane < n_boxes)
-        tma_load_2d(base + Cfg::kKOff + s * Cfg::kTileBytes + dst_off, &k_map, &k_full[s], hh * 64, row);
+        tma_load_2d(base + Cfg::kKOff + sk * Cfg::kTileBytes + dst_off, &k_map, &k_full[sk], hh * 64, row);
       // V block j
-      if (j >= S) tc_wait(&v_empty[s], par, a.status, 510 + s, abort_flag);
-      if (lane == 0) mbar_arrive_expect_tx(&v_full[s], Cfg::kTileBytes);
+      if (j >= SV) tc_wait(&v_empty[sv], ((j / SV) - 1) & 1, a.status, 510 + sv, abort_flag);
+      // the general query prologue stages its rows in the last V stage: keep out until it is done
+      if (!fast_prologue && j == SV - 1) tc_wait(q_ready, 0, a.status, 515, abort_flag);
+      if (lane == 0) mbar_arrive_expect_tx(&v_full[sv], Cfg::kTileBytes);
       __syncwarp();
       if (lane < n_boxes)
-        tma_load_2d(base + Cfg::kVOff + s * Cfg::kTileBytes + dst_off, &v_map, &v_full[s], hh * 64, row);
+        tma_load_2d(base + Cfg::kVOff + sv * Cfg::kTileBytes + dst_off, &v_map, &v_full[sv], hh * 64, row);
       __syncwarp();
     }
   } else if (warp == 9) {
@@ -351,7 +358,7 @@ __global__ void __launch_bounds__(384, 1)
       constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
       auto issue_qk = [&](int t, int j) {
         const uint32_t a_base = base + Cfg::kQOff + t * Cfg::kTileBytes;
-        const uint32_t b_base = base + Cfg::kKOff + (j % S) * Cfg::kTileBytes;
+        const uint32_t b_base = base + Cfg::kKOff + (j % SK) * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * Cfg::kHalfBytes + (ks & 3) * 32;
@@ -360,7 +367,7 @@ __global__ void __launch_bounds__(384, 1)
         }
       };
       auto issue_pv = [&](int t, int j) {
-        const uint32_t b_base = base + Cfg::kVOff + (j % S) * Cfg::kTileBytes;
+        const uint32_t b_base = base + Cfg::kVOff + (j % SV) * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           tc_mma_ts(tmem + Cfg::kColO + t * HD, tmem + Cfg::kColS + t * 128 + ks * 8,
@@ -384,11 +391,11 @@ __global__ void __launch_bounds__(384, 1)
         for (int t = 0; t < 2; ++t) {
           if (j >= n_blk[t]) continue;
           tc_wait(&p_full[t], j & 1, a.status, 530 + t, abort_flag);
-          tc_wait(&v_full[j % S], (j / S) & 1, a.status, 532, abort_flag);
+          tc_wait(&v_full[j % SV], (j / SV) & 1, a.status, 532, abort_flag);
           tc_fence_after();
           issue_pv(t, j);
           if (j + 1 < n_blk[t]) {
-            tc_wait(&k_full[(j + 1) % S], ((j + 1) / S) & 1, a.status, 533, abort_flag);
+            tc_wait(&k_full[(j + 1) % SK], ((j + 1) / SK) & 1, a.status, 533, abort_flag);
             tc_fence_after();
             issue_qk(t, j + 1);
             tc_commit(&s_full[t]);
@@ -397,8 +404,8 @@ __global__ void __launch_bounds__(384, 1)
             tc_commit(&o_full[t]);
           }
         }
-        tc_commit(&v_empty[j % S]);
-        if (next_qk) tc_commit(&k_empty[(j + 1) % S]);
+        tc_commit(&v_empty[j % SV]);
+        if (next_qk) tc_commit(&k_empty[(j + 1) % SK]);
       }
     }
     __syncwarp();
@@ -419,7 +426,7 @@ __global__ void __launch_bounds__(384, 1)
     {
       const uint32_t q_tile = base + Cfg::kQOff + t * Cfg::kTileBytes;
       constexpr int VEC = HD / 32;
-      const bool fast = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
+      const bool fast = fast_prologue;
       float* xrow = reinterpret_cast<float*>(gen + Cfg::kRowOff) + warp * HD;
       if (fast) {
         // R rows per pass with all their global loads issued before any arithmetic: a warp that walked
