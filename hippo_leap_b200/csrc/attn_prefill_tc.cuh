@@ -603,47 +603,70 @@ __global__ void __launch_bounds__(384, 1)
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool live = trow < a.n_tok;
+      // fp16 output with contiguous head rows goes through shared memory (this tile's Q area, idle now
+      // that its last Q K^T has completed), so that whole 256-byte rows leave in coalesced 16-byte
+      // lanes -- which matters most for the peer destinations, where a 16-byte store per row would
+      // waste most of every NVLink packet.
+      const bool staged = a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16 && (a.out.ts & 7) == 0 && (a.out.hs & 7) == 0 &&
+                          (reinterpret_cast<uintptr_t>(a.out.ptr) & 15) == 0;
+      const uint32_t o_tile = base + Cfg::kQOff + t * Cfg::kTileBytes;  // [128 rows][HD halfs], 16-byte chunks XOR-swizzled
 #pragma unroll
       for (int q4 = 0; q4 < HD / 32; ++q4) {
         float oreg[32];
         tc_ld32f(tO + q4 * 32, oreg);
         tc_wait_ld();
-        if (live) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) oreg[i] *= inv;
-          if (a.gate.ptr != nullptr) {
+        for (int i = 0; i < 32; ++i) oreg[i] *= inv;
+        if (live && a.gate.ptr != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) oreg[i] = apply_gate(a.gate, trow, h, q4 * 32 + i, oreg[i]);
+          for (int i = 0; i < 32; ++i) oreg[i] = apply_gate(a.gate, trow, h, q4 * 32 + i, oreg[i]);
+        }
+        if (staged) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            const int chunk = (q4 * 4 + (i >> 3)) ^ (r & (HD / 8 - 1));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(o_tile + r * (HD * 2) + chunk * 16),
+                         "r"(pack_half2(oreg[i], oreg[i + 1])), "r"(pack_half2(oreg[i + 2], oreg[i + 3])),
+                         "r"(pack_half2(oreg[i + 4], oreg[i + 5])), "r"(pack_half2(oreg[i + 6], oreg[i + 7]))
+                         : "memory");
           }
+        } else if (live) {
           const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(h) * a.out.hs + q4 * 32;
           for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {  // destination 0 is the local output
             void* obase = dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1];
             if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
               __half* dst = static_cast<__half*>(obase) + off;
-              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8)
-                  *reinterpret_cast<uint4*>(dst + i) = make_uint4(
-                      pack_half2(oreg[i], oreg[i + 1]), pack_half2(oreg[i + 2], oreg[i + 3]),
-                      pack_half2(oreg[i + 4], oreg[i + 5]), pack_half2(oreg[i + 6], oreg[i + 7]));
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2)
-                  *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i], oreg[i + 1]);
-              }
+              for (int i = 0; i < 32; i += 2) *reinterpret_cast<uint32_t*>(dst + i) = pack_half2(oreg[i], oreg[i + 1]);
             } else if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F32 &&
                        (reinterpret_cast<uintptr_t>(static_cast<float*>(obase) + off) & 15) == 0) {
               float* dst = static_cast<float*>(obase) + off;
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(dst + i) =
-                    make_float4(oreg[i], oreg[i + 1], oreg[i + 2], oreg[i + 3]);
+                *reinterpret_cast<float4*>(dst + i) = make_float4(oreg[i], oreg[i + 1], oreg[i + 2], oreg[i + 3]);
             } else {
               View ov = a.out;
               ov.ptr = obase;
 #pragma unroll
               for (int i = 0; i < 32; ++i) view_store(ov, trow, h, q4 * 32 + i, oreg[i]);
             }
+          }
+        }
+      }
+      if (staged) {
+        named_bar_sync(1 + t, 128);  // the tile's 128 rows are in shared memory
+        constexpr int kChunks = HD / 8;  // 16-byte chunks per row
+        const int rows_live = min(128, a.n_tok - (t0 + 128 * t));
+        for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {
+          __half* obase = static_cast<__half*>(dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1]) +
+                          static_cast<int64_t>(h) * a.out.hs;
+          for (int idx = r; idx < rows_live * kChunks; idx += 128) {
+            const int row = idx / kChunks, ch = idx % kChunks;
+            uint4 val;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                         : "r"(o_tile + row * (HD * 2) + ((ch ^ (row & (kChunks - 1))) * 16)));
+            *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(t0 + 128 * t + row) * a.out.ts + ch * 8) = val;
           }
         }
       }

@@ -637,8 +637,11 @@ extern "C" int32_t hl_b200_attn_prefill_bcast(hl_ctx* ctx, hl_kv* kv, int32_t la
   if (!ctx) return HL_ERR_ARG;
   if (n_peers < 0 || n_peers > 7) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: n_peers %d outside [0, 7]", n_peers);
   if (n_peers > 0 && !peer_out_ptrs) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: null peer pointer list");
-  for (int i = 0; i < n_peers; ++i)
+  for (int i = 0; i < n_peers; ++i) {
     if (!peer_out_ptrs[i]) return hl_fail(ctx, HL_ERR_ARG, "prefill_bcast: null peer pointer %d", i);
+    if (reinterpret_cast<uintptr_t>(peer_out_ptrs[i]) % 16 != 0 || (out && reinterpret_cast<uintptr_t>(out->ptr) % 16 != 0))
+      return hl_fail(ctx, HL_ERR_ALIGN, "prefill_bcast: output pointers must be 16-byte aligned");
+  }
   return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, peer_out_ptrs,
                       n_peers, gpu_ms);
 }
