@@ -46,6 +46,7 @@ BACKEND_SYMBOLS = {
     "hl_backend_forward_decode": (_i32, [_i32, C.POINTER(KvCacheC), _f32p]),
     "hl_backend_forward_decode_token": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32)]),
     "hl_backend_forward_decode_token_timed": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32), _f32p]),
+    "hl_backend_set_decode_graph": (_i32, [_i32]),
     "hl_backend_last_error": (C.c_char_p, []),
     "hl_backend_launch_count": (C.c_int64, []),
 }
@@ -192,5 +193,47 @@ def argmaxLast(logits: np.ndarray, nVocab: int) -> int:
     raise ValueError("logits shape mismatch for vocab")
 
 
+def setDecodeGraph(enabled: bool):
+    """forwardDecodeToken[Timed]: replay a captured CUDA graph per token (default) or launch kernel by kernel."""
+    _check(_lib().hl_backend_set_decode_graph(int(enabled)))
+
+
 def launchCount() -> int:
     return _lib().hl_backend_launch_count()
+
+
+@dataclass
+class GenerateResult:
+    """GenerateResult of the reference (src/hippo_leap/inference.nim:17-23), token ids instead of text."""
+    tokens: list
+    promptTokens: int
+    completionTokens: int
+    totalTokens: int
+    elapsedMs: float
+    gpuMs: float
+
+
+def generate(m: Model, cache: KvCache, promptTokens, maxTokens: int, maxContextLen: int | None = None,
+             stopTokenIds=()) -> GenerateResult:
+    """The reference's generate loop (src/hippo_leap/inference.nim:51-97) on token ids: reset curLen,
+    one prefill, argmax, then forwardDecodeTokenTimed until maxTokens or a stop token."""
+    import time
+    t0 = time.perf_counter()
+    cache.curLen = 0
+    prompt = list(promptTokens)
+    if not prompt:
+        return GenerateResult([], 0, 0, 0, 0.0, 0.0)
+    max_ctx = cache.maxLen if maxContextLen is None else maxContextLen
+    max_gen = min(maxTokens, max_ctx - len(prompt))
+    if max_gen <= 0:
+        return GenerateResult([], len(prompt), 0, len(prompt), 0.0, 0.0)
+    nxt = argmaxLast(forwardPrefill(m, prompt, cache), m.hparams.nVocab)
+    generated, gpu_ms = [nxt], 0.0
+    for _ in range(1, max_gen):
+        if nxt in stopTokenIds:
+            break
+        nxt, ms = forwardDecodeTokenTimed(m, nxt, cache)
+        gpu_ms += ms
+        generated.append(nxt)
+    return GenerateResult(generated, len(prompt), len(generated), len(prompt) + len(generated),
+                          (time.perf_counter() - t0) * 1e3, gpu_ms)

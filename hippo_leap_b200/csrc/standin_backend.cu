@@ -31,6 +31,11 @@ struct Backend {
   int table_len = 0;
   int32_t* next_d = nullptr;
   int32_t* status_h = nullptr;  // pinned copy of the device status word
+  int32_t* step_h = nullptr;    // pinned {token id, ctx_len, next token}: inputs / output of the replayed decode graph
+  cudaGraphExec_t graph = nullptr;  // one decode step (all layers) captured once per (cache, max_len)
+  const void* graph_kv = nullptr;
+  int graph_max_len = 0;
+  bool use_graph = true;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   std::string err;
 } g;
@@ -70,12 +75,16 @@ int32_t ensure_ctx(int device) {
   return HL_OK;
 }
 
-// rows of the per-layer tables selected by the token ids: dst[t][:] = table[token[t]][:]
-__global__ void gather_rows_kernel(const float* __restrict__ table, const int32_t* __restrict__ tokens, int dim,
-                                   int n_vocab, float* __restrict__ dst) {
-  const int t = blockIdx.x;
+// the three lookups of one layer in one launch: blockIdx.y = 0 / 1 / 2 selects q / k / v
+__global__ void gather_qkv_kernel(const float* __restrict__ eq, const float* __restrict__ ek,
+                                  const float* __restrict__ ev, const int32_t* __restrict__ tokens, int qd, int kd,
+                                  int n_vocab, float* __restrict__ q, float* __restrict__ k, float* __restrict__ v) {
+  const int t = blockIdx.x, which = blockIdx.y;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
+  const int dim = which == 0 ? qd : kd;
+  const float* table = which == 0 ? eq : (which == 1 ? ek : ev);
+  float* dst = which == 0 ? q : (which == 1 ? k : v);
   const float4* src = reinterpret_cast<const float4*>(table + static_cast<int64_t>(tok) * dim);
   float4* d = reinterpret_cast<float4*>(dst + static_cast<int64_t>(t) * dim);
   for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) d[i] = src[i];
@@ -172,7 +181,12 @@ hl_attn_shape shape_for_layer(int l) {
 }
 
 // One forward over n tokens starting at position pos0; decode is n == 1.
-int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode) {
+// `grid_ctx` sizes the decode grid and scratch (>= the real context); with `from_step_h` the token id and
+// the context length are read from the pinned step buffer by copy nodes, so that a captured graph of
+// this sequence can be replayed for every token (the reference's megakernel backend replays a HIP
+// graph fed by a device-side step record the same way: backends/megakernel.nim:78-83, 2458-2479).
+int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode, int grid_ctx = 0,
+                bool from_step_h = false) {
   hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
   const int qd = g.hp.n_head * g.hp.head_dim, kd = g.hp.n_head_kv * g.hp.head_dim;
   B_CUDA(cudaSetDevice(g.device));
@@ -185,21 +199,29 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     g.tokens_cap = n;
   }
   cudaStream_t st = g.ctx->stream;
-  B_CUDA(cudaMemcpyAsync(g.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  if (decode) set_i32_kernel<<<1, 1, 0, st>>>(g.ctx_len_d, pos0 + 1);
+  if (from_step_h) {
+    B_CUDA(cudaMemcpyAsync(g.tokens_d, &g.step_h[0], sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    B_CUDA(cudaMemcpyAsync(g.ctx_len_d, &g.step_h[1], sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  } else {
+    B_CUDA(cudaMemcpyAsync(g.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    if (decode) {
+      set_i32_kernel<<<1, 1, 0, st>>>(g.ctx_len_d, pos0 + 1);
+      g.ctx->launches += 1;
+    }
+  }
+  if (grid_ctx < pos0 + 1) grid_ctx = pos0 + 1;
   const int64_t layer_stride = static_cast<int64_t>(g.act_cap) * qd;
   for (int l = 0; l < g.hp.n_layer; ++l) {
     const size_t toff = static_cast<size_t>(l) * g.hp.n_vocab;
-    gather_rows_kernel<<<n, 128, 0, st>>>(g.eq + toff * qd, g.tokens_d, qd, g.hp.n_vocab, g.q);
-    gather_rows_kernel<<<n, 128, 0, st>>>(g.ek + toff * kd, g.tokens_d, kd, g.hp.n_vocab, g.k);
-    gather_rows_kernel<<<n, 128, 0, st>>>(g.ev + toff * kd, g.tokens_d, kd, g.hp.n_vocab, g.v);
-    g.ctx->launches += 3;
+    gather_qkv_kernel<<<dim3(n, 3), 128, 0, st>>>(g.eq + toff * qd, g.ek + toff * kd, g.ev + toff * kd, g.tokens_d, qd,
+                                                   kd, g.hp.n_vocab, g.q, g.k, g.v);
+    g.ctx->launches += 1;
     const hl_attn_shape s = shape_for_layer(l);
     hl_view qv{g.q, HL_DTYPE_F32, qd, g.hp.head_dim, 1}, kv_{g.k, HL_DTYPE_F32, kd, g.hp.head_dim, 1},
         vv{g.v, HL_DTYPE_F32, kd, g.hp.head_dim, 1}, ov{g.out + l * layer_stride, HL_DTYPE_F32, qd, g.hp.head_dim, 1};
     if (decode) {
       B_TRY(hl_b200_kv_append_batch(g.ctx, kv, l, &s, &kv_, &vv, 1, g.ctx_len_d, g.table_d, g.table_len));
-      B_TRY(hl_b200_attn_decode(g.ctx, kv, l, &s, &qv, 1, g.ctx_len_d, pos0 + 1, g.table_d, g.table_len, &ov, nullptr));
+      B_TRY(hl_b200_attn_decode(g.ctx, kv, l, &s, &qv, 1, g.ctx_len_d, grid_ctx, g.table_d, g.table_len, &ov, nullptr));
     } else {
       B_TRY(hl_b200_kv_append_seq(g.ctx, kv, l, &s, &kv_, &vv, n, pos0, g.table_d, g.table_len));
       B_TRY(hl_b200_attn_prefill(g.ctx, kv, l, &s, &qv, n, pos0, g.table_d, g.table_len, &ov, nullptr));
@@ -290,7 +312,8 @@ extern "C" int32_t hl_backend_load_model(int32_t device, const hl_hparams* hp, c
   if (ok && w->k_norm) ok = up(&g.kn, w->k_norm, static_cast<size_t>(hp->n_layer) * hp->head_dim);
   ok = ok && cudaMalloc(&g.logits_d, hp->n_vocab * sizeof(float)) == cudaSuccess &&
        cudaMalloc(&g.ctx_len_d, sizeof(int32_t)) == cudaSuccess && cudaMalloc(&g.next_d, sizeof(int32_t)) == cudaSuccess &&
-       cudaMallocHost(&g.status_h, 2 * sizeof(int32_t)) == cudaSuccess && cudaEventCreate(&g.e0) == cudaSuccess &&
+       cudaMallocHost(&g.status_h, 2 * sizeof(int32_t)) == cudaSuccess &&
+       cudaMallocHost(&g.step_h, 4 * sizeof(int32_t)) == cudaSuccess && cudaEventCreate(&g.e0) == cudaSuccess &&
        cudaEventCreate(&g.e1) == cudaSuccess;
   if (!ok) {
     cudaGetLastError();
@@ -322,6 +345,11 @@ extern "C" int32_t hl_backend_unload_model(void) {
   }
   if (g.status_h) cudaFreeHost(g.status_h);
   g.status_h = nullptr;
+  if (g.step_h) cudaFreeHost(g.step_h);
+  g.step_h = nullptr;
+  if (g.graph) cudaGraphExecDestroy(g.graph);
+  g.graph = nullptr;
+  g.graph_kv = nullptr;
   if (g.e0) cudaEventDestroy(g.e0);
   if (g.e1) cudaEventDestroy(g.e1);
   g.e0 = g.e1 = nullptr;
@@ -361,9 +389,76 @@ extern "C" int32_t hl_backend_forward_decode(int32_t token, hl_kv_cache* cache, 
   return HL_OK;
 }
 
+// Capture one whole decode step (every layer + logits + argmax + the result copies) into a CUDA graph.
+// The grid and the split-KV scratch are sized for the cache's full capacity, so the same graph serves
+// every position: CTAs of chunks beyond the current context exit at once.
+static int32_t ensure_decode_graph(hl_kv_cache* cache) {
+  if (g.graph && g.graph_kv == cache->gpu_cache && g.graph_max_len == cache->max_len) return HL_OK;
+  if (g.graph) cudaGraphExecDestroy(g.graph);
+  g.graph = nullptr;
+  cudaStream_t st = g.ctx->stream;
+  // An uncaptured pass first: it configures the kernels and grows every scratch buffer to its final size,
+  // so nothing allocates or synchronises while the stream is being captured.  It runs at the caller's
+  // current position and is simply repeated by the first replay (same position, same values).
+  B_PASS(forward(nullptr, 1, g.step_h[1] - 1, cache, true, cache->max_len, true));
+  B_CUDA(cudaStreamSynchronize(st));
+  B_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  int32_t rc = forward(nullptr, 1, g.step_h[1] - 1, cache, true, cache->max_len, true);
+  if (rc == HL_OK) {
+    argmax_first_kernel<<<1, 256, 0, st>>>(g.logits_d, g.hp.n_vocab, g.next_d);
+    g.ctx->launches += 1;
+    cudaMemcpyAsync(&g.step_h[2], g.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    cudaMemcpyAsync(g.status_h, g.ctx->status_d, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  }
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(st, &graph);
+  if (rc != HL_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess || !graph) return bfail(HL_ERR_CUDA, "stream capture of the decode step failed");
+  e = cudaGraphInstantiate(&g.graph, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return bfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
+  g.graph_kv = cache->gpu_cache;
+  g.graph_max_len = cache->max_len;
+  return HL_OK;
+}
+
+static int32_t decode_token_graph(int32_t token, hl_kv_cache* cache, int32_t* next_token, float* gpu_ms) {
+  B_PASS(check_cache(cache));
+  if (cache->cur_len >= cache->max_len) return bfail(HL_ERR_CAPACITY, "KV cache full");
+  if (cache->cur_len < 0) return bfail(HL_ERR_ARG, "negative cur_len");
+  B_CUDA(cudaSetDevice(g.device));
+  g.step_h[0] = token;
+  g.step_h[1] = cache->cur_len + 1;
+  B_PASS(ensure_decode_graph(cache));
+  cudaStream_t st = g.ctx->stream;
+  if (gpu_ms) B_CUDA(cudaEventRecord(g.e0, st));
+  B_CUDA(cudaGraphLaunch(g.graph, st));
+  if (gpu_ms) B_CUDA(cudaEventRecord(g.e1, st));
+  B_CUDA(cudaStreamSynchronize(st));
+  g.ctx->launches += 3 * g.hp.n_layer + g.hp.n_layer + 2;  // kernels inside one replay (combine counted once per layer)
+  if (g.status_h[0] != 0) {
+    const int32_t code = g.status_h[0];
+    cudaMemset(g.ctx->status_d, 0, 2 * sizeof(int32_t));
+    return bfail(code, "a device-side check failed during the decode step");
+  }
+  if (gpu_ms) B_CUDA(cudaEventElapsedTime(gpu_ms, g.e0, g.e1));
+  *next_token = g.step_h[2];
+  cache->cur_len += 1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_backend_set_decode_graph(int32_t enabled) {
+  g.use_graph = enabled != 0;
+  return HL_OK;
+}
+
 extern "C" int32_t hl_backend_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token,
                                                          float* gpu_ms) {
   if (!next_token) return bfail(HL_ERR_ARG, "null next_token");
+  if (g.use_graph && g.loaded) return decode_token_graph(token, cache, next_token, gpu_ms);
   B_PASS(check_cache(cache));
   if (gpu_ms) B_CUDA(cudaEventRecord(g.e0, g.ctx->stream));
   B_PASS(decode_common(token, cache));

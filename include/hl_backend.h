@@ -73,6 +73,10 @@ int32_t hl_backend_forward_decode_token(int32_t token, hl_kv_cache* cache, int32
 /* forwardDecodeTokenTimed(m, token, cache, gpuMs): megakernel.nim:2514-2529. */
 int32_t hl_backend_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token,
                                               float* gpu_ms);
+/* forwardDecodeToken[Timed] replay one captured CUDA graph per token by default (the counterpart of the
+ * megakernel backend's graph mode, -d:useGraphCapture, megakernel.nim:2458-2479); 0 switches to plain
+ * launches.  Results are identical either way. */
+int32_t hl_backend_set_decode_graph(int32_t enabled);
 const char* hl_backend_last_error(void);
 /* Kernel launches issued by the backend's context so far. */
 int64_t hl_backend_launch_count(void);

@@ -137,3 +137,56 @@ def test_bad_hparams_rejected_before_any_launch():
     with pytest.raises(ValueError, match="head_dim"):
         B.initKvCache(hp, 32)
     B.unloadModelBackend()
+
+
+def test_generate_loop_and_bench_cli(capsys):
+    """generate() follows the reference loop (inference.nim:51-97) and the bench command prints the
+    reference's table (cmd_bench.nim:101-136)."""
+    from hippo_leap_b200 import cmd_bench
+    hp = B.HParams(nVocab=512, nLayer=2, nHead=8, nHeadKv=2, headDim=64)
+    m = B.standin_model(hp, 9)
+    cache = B.initKvCache(hp, 64)
+    B.loadModelBackend(m, hp)
+    try:
+        res = B.generate(m, cache, [1, 2, 3, 4], 8)
+        assert res.promptTokens == 4 and res.completionTokens == 8 and res.totalTokens == 12
+        assert res.elapsedMs > 0 and res.gpuMs > 0 and cache.curLen == 4 + 7
+        again = B.generate(m, cache, [1, 2, 3, 4], 8)
+        assert again.tokens == res.tokens                      # curLen reset -> same request, same stream
+        assert B.generate(m, cache, [], 8).completionTokens == 0
+        assert B.generate(m, cache, list(range(64)), 8).completionTokens == 0   # no room left in the context
+        stop = res.tokens[2]
+        assert B.generate(m, cache, [1, 2, 3, 4], 8, stopTokenIds=(stop,)).tokens == res.tokens[:res.tokens.index(stop) + 1]
+    finally:
+        B.freeKvCache(cache)
+        B.unloadModelBackend()
+    assert cmd_bench.main(["--config", "1", "--prompt-tokens", "32", "--tokens", "8", "--runs", "2", "--warmup", "1",
+                           "--context", "64"]) == 0
+    out = capsys.readouterr().out
+    assert " Run  Tokens  Time(ms)   tok/s   GPU(ms)  gpu tok/s" in out
+    assert "Wall:" in out and "GPU :" in out and "±" in out
+
+
+def test_decode_graph_replay_equals_plain_launches():
+    """forwardDecodeToken through the captured CUDA graph and through plain launches give the same ids,
+    across a reset of curLen and a second cache (the graph is re-captured for another cache)."""
+    hp = B.HParams(nVocab=512, nLayer=3, nHead=16, nHeadKv=4, headDim=128, ropeFreqBase=5e5)
+    m = B.standin_model(hp, 12)
+    cache = B.initKvCache(hp, 200)
+    B.loadModelBackend(m, hp)
+    try:
+        prompt = list(range(7, 7 + 90))
+        streams = {}
+        for mode in (True, False, True):
+            B.setDecodeGraph(mode)
+            res = B.generate(m, cache, prompt, 60)
+            streams.setdefault(mode, []).append(res.tokens)
+        assert streams[True][0] == streams[False][0] == streams[True][1]
+        cache2 = B.initKvCache(hp, 120)
+        B.setDecodeGraph(True)
+        assert B.generate(m, cache2, prompt, 25).tokens == streams[True][0][:25]
+        B.freeKvCache(cache2)
+    finally:
+        B.setDecodeGraph(True)
+        B.freeKvCache(cache)
+        B.unloadModelBackend()
