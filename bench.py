@@ -244,6 +244,26 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
     return res
 
 
+def extra_linear(ctx, torch, device, peaks):
+    """The dense fp16 projection next to the hot path: Wo-shaped GEMM at config 3 size and its decode GEMV."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7)
+    res = {}
+    for name, (M, N, K) in {"gemm_8192x4096x4096": (8192, 4096, 4096), "gemv_1x4096x4096": (1, 4096, 4096)}.items():
+        a = torch.randn((M, K), generator=gen, device=device).half()
+        w = (torch.randn((N, K), generator=gen, device=device) / K ** 0.5).half()
+        out = torch.empty((M, N), dtype=torch.float32, device=device)
+        for _ in range(3):
+            ctx.linear_f16(a, w, out)
+        n = 20
+        ms = timed_loop(torch, lambda: ctx.linear_f16(a, w, out), n) / n
+        fl = 2.0 * M * N * K
+        by = (M * K + N * K) * 2 + M * N * 4
+        res[name] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"],
+                     "gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    return res
+
+
 def extra_config2_pipeline(torch, device_index):
     """Config 2 end to end through the backend contract (the calls hippo_leap's generate loop makes):
     one 2048-token prefill, then 256 greedy decode steps, 16 attention layers, llama3-scaled theta,
@@ -356,6 +376,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-chunk", type=int, default=0)
     ap.add_argument("--prefill-kernel", type=int, default=0, help="0 auto, 1 warp-MMA, 2 tcgen05, 3 tcgen05 on SM pairs")
+    ap.add_argument("--linear-only", action="store_true", help="measure only the dense fp16 projection kernels")
     ap.add_argument("--pipeline-only", action="store_true", help="measure only the config 2 backend pipeline")
     ap.add_argument("--head-sharded-only", action="store_true",
                     help="measure only the head-sharded config 5 prefill + all-gather at N GPUs")
@@ -387,6 +408,10 @@ def main():
     cfg = synth.CONFIGS[4]
     ctx = hl.Context(local_rank, torch.cuda.current_stream())
     ctx.set_tuning(args.decode_chunk, args.prefill_kernel)
+    if args.linear_only:
+        print(json.dumps(extra_linear(ctx, torch, device, peaks)), file=result_out, flush=True)
+        ctx.close()
+        return
     if args.pipeline_only:
         print(json.dumps(extra_config2_pipeline(torch, local_rank)), file=result_out, flush=True)
         ctx.close()
@@ -468,6 +493,7 @@ def main():
         if world == 1:
             extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False))
             extra["config2_backend_pipeline"] = extra_config2_pipeline(torch, local_rank)
+            extra["linear_f16"] = extra_linear(ctx, torch, device, peaks)
         if cfg.n_head_kv % world == 0:
             extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
                                                                                peaks)

@@ -19,6 +19,7 @@
 #include "attn_prefill_tc2.cuh"
 #include "host_common.h"
 #include "kv_append.cuh"
+#include "linear_f16.cuh"
 
 using namespace hl;
 
@@ -653,4 +654,74 @@ extern "C" int32_t hl_b200_attn_prefill_gated(hl_ctx* ctx, hl_kv* kv, int32_t la
   if (ctx && !gate) return hl_fail(ctx, HL_ERR_ARG, "prefill_gated: null gate view");
   return prefill_impl(ctx, kv, layer, s, q, n_tok, start_pos, block_table, n_blocks_in_table, out, nullptr, 0, gpu_ms,
                       gate);
+}
+
+// ---------------------------------------------------------------------------------------------
+// dense fp16 projection: out = A . W^T (+ residual)
+// ---------------------------------------------------------------------------------------------
+static int32_t make_map_2d(hl_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                           int box_rows) {
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return hl_fail(ctx, HL_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return HL_OK;
+}
+
+extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out,
+                                      int32_t out_dtype, int64_t ldo, const float* resid, int64_t ldr, int32_t M,
+                                      int32_t N, int32_t K, float* gpu_ms) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!a || !w || !out) return hl_fail(ctx, HL_ERR_ARG, "linear: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return hl_fail(ctx, HL_ERR_ARG, "linear: non-positive size");
+  if (out_dtype != HL_DTYPE_F32 && out_dtype != HL_DTYPE_F16) return hl_fail(ctx, HL_ERR_ARG, "linear: bad out dtype");
+  if (lda < K || ldw < K || ldo < N || (resid && ldr < N)) return hl_fail(ctx, HL_ERR_ARG, "linear: leading dimension too small");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  LinearArgs g{};
+  g.a = static_cast<const __half*>(a);
+  g.w = static_cast<const __half*>(w);
+  g.out = out;
+  g.resid = resid;
+  g.lda = lda;
+  g.ldw = ldw;
+  g.ldo = ldo;
+  g.ldr = ldr;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.out_dtype = out_dtype;
+  g.status = ctx->status_d;
+  int32_t rc = hl_begin_timing(ctx, gpu_ms);
+  if (rc != HL_OK) return rc;
+  if (M < 16) {
+    const unsigned grid = static_cast<unsigned>((static_cast<int64_t>(N) * 32 + 255) / 256);
+    if (M <= 4)
+      linear_gemv_kernel<4><<<grid, 256, 0, ctx->stream>>>(g);
+    else
+      linear_gemv_kernel<16><<<grid, 256, 0, ctx->stream>>>(g);
+  } else {
+    if ((lda & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+      return hl_fail(ctx, HL_ERR_ALIGN, "linear: A and W need 16-byte aligned bases and row strides (multiples of 8 halfs)");
+    using Cfg = LinearGemmCfg;
+    static bool configured[16] = {};
+    if (!configured[ctx->device & 15]) {
+      HL_CUDA(ctx, cudaFuncSetAttribute(linear_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      configured[ctx->device & 15] = true;
+    }
+    CUtensorMap a_map, w_map;
+    rc = make_map_2d(ctx, &a_map, a, M, K, lda, Cfg::BM);
+    if (rc == HL_OK) rc = make_map_2d(ctx, &w_map, w, N, K, ldw, Cfg::BN);
+    if (rc != HL_OK) return rc;
+    const int n_tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + Cfg::BN - 1) / Cfg::BN);
+    const int grid = n_tiles < ctx->n_sm ? n_tiles : ctx->n_sm;
+    linear_gemm_kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(a_map, w_map, g);
+  }
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return hl_end_timing(ctx, gpu_ms);
 }

@@ -280,3 +280,23 @@ class Context:
             _i32_dev(block_table), block_table.numel(), C.byref(oc), arr, len(peer_ptrs),
             C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
+
+    def linear_f16(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                   resid: torch.Tensor | None = None, out_dtype=torch.float32, timed: bool = False):
+        """out[M, N] = a[M, K] @ w[N, K].T (+ resid): fp16 inputs, fp32 accumulation (hl_b200_linear_f16)."""
+        assert a.is_cuda and w.is_cuda and a.dtype == torch.float16 and w.dtype == torch.float16
+        assert a.dim() == 2 and w.dim() == 2 and a.stride(1) == 1 and w.stride(1) == 1 and a.shape[1] == w.shape[1]
+        M, K = a.shape
+        N = w.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        assert out.stride(1) == 1 and out.shape == (M, N)
+        if resid is not None:
+            assert resid.dtype == torch.float32 and resid.stride(1) == 1 and resid.shape == (M, N)
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_linear_f16(
+            self.handle, a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+            L.HL_DTYPE_F32 if out.dtype == torch.float32 else L.HL_DTYPE_F16, out.stride(0),
+            None if resid is None else resid.data_ptr(), 0 if resid is None else resid.stride(0), M, N, K,
+            C.byref(ms) if timed else None))
+        return (out, ms.value) if timed else out

@@ -217,6 +217,17 @@ int32_t hl_b200_decode_step_host(hl_ctx* ctx, hl_kv* kv, int32_t layer,
                                  int32_t max_ctx_h, const int32_t* block_tables,
                                  int32_t max_blocks_per_seq, float* out_h, float* gpu_ms);
 
+/* ---- projections either side of attention -------------------------------------------------
+ * out[M, N] = A[M, K] . W[N, K]^T (+ residual[M, N]), fp16 A and W (row-major, leading dimensions in
+ * elements), fp32 accumulation, fp32 or fp16 out.  Replaces gpuLinearCol for dense weights
+ * (naive.nim:3466-3547: out[row, t] = sum_k W[row, k] x[k, t]); the residual add replaces the gpuAdd
+ * that follows the output and down projections (naive.nim:4080, 4086).  M >= 16 runs a tcgen05 GEMM,
+ * smaller M a weight-bandwidth-bound GEMV.  This is the first piece of the layers around the hot
+ * path; the quantised GEMV family of the reference (naive.nim:354-1917) is not reproduced. */
+int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out,
+                           int32_t out_dtype, int64_t ldo, const float* resid, int64_t ldr, int32_t M,
+                           int32_t N, int32_t K, float* gpu_ms);
+
 /* No counterpart in the reference.  Self-test of the bounded-wait machinery: launches one CTA that
  * waits, for at most `max_polls` polls, on a barrier nothing ever signals.  The wait gives up,
  * the kernel returns normally, and hl_b200_device_status then reports {HL_ERR_TIMEOUT, 900}.  The

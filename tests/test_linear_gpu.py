@@ -1,0 +1,69 @@
+"""The dense fp16 projection (hl_b200_linear_f16) against the oracle's matmul (tensor.nim:63-81) on the
+fp16-rounded operands: tcgen05 GEMM for prefill-sized M, GEMV for decode-sized M, ragged edges, residual,
+and the attention -> output-projection hand-off in fp16."""
+import numpy as np
+import pytest
+import torch
+
+import hippo_leap_b200 as hl
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(hl_ctx, M, N, K, resid, out_dtype, seed=0):
+    g = np.random.Generator(np.random.PCG64([seed, M, N, K]))
+    a = g.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+    w = (g.standard_normal((N, K), dtype=np.float32) / np.sqrt(K)).astype(np.float16)
+    r = g.standard_normal((M, N), dtype=np.float32) if resid else None
+    out = hl_ctx.linear_f16(torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda(),
+                            resid=None if r is None else torch.from_numpy(r).cuda(), out_dtype=out_dtype)
+    got = out.float().cpu().numpy()
+    want = oracle.matmul(a.astype(np.float32), np.ascontiguousarray(w.astype(np.float32).T))
+    if r is not None:
+        want = want + r
+    tol = 2e-3 if out_dtype == torch.float16 else 2e-4 * max(1.0, np.sqrt(K / 256))
+    err = float(np.abs(got - want).max())
+    assert err < tol * max(1.0, float(np.abs(want).max())), f"M={M} N={N} K={K}: max-abs {err:.3e}"
+    assert hl_ctx.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (2048, 2048, 2048), (200, 300, 72),
+                                   (17, 5, 8), (1000, 256, 4096), (129, 257, 200)])
+def test_gemm_against_oracle_matmul(hl_ctx, M, N, K):
+    _check(hl_ctx, M, N, K, resid=False, out_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (3, 512, 1000), (8, 130, 64), (15, 64, 4096)])
+def test_gemv_against_oracle_matmul(hl_ctx, M, N, K):
+    _check(hl_ctx, M, N, K, resid=True, out_dtype=torch.float32)
+
+
+def test_residual_and_fp16_output(hl_ctx):
+    _check(hl_ctx, 384, 512, 256, resid=True, out_dtype=torch.float32, seed=3)
+    _check(hl_ctx, 384, 512, 256, resid=False, out_dtype=torch.float16, seed=4)
+
+
+def test_attention_output_feeds_the_projection_in_fp16(hl_ctx):
+    """fp16 attention output, token-major [S, n_head*hd], straight into the Wo GEMM (naive.nim:4079)."""
+    from hippo_leap_b200 import synth
+    from tests.helpers import oracle_seq
+    cfg = synth.CONFIGS[1]
+    S, bt, n_emb = 256, 16, 512
+    q, k, v = synth.gen_qkv(cfg, S)
+    theta = cfg.theta()
+    hl_ctx.set_rope(theta)
+    shape = hl.AttnShape(cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF)
+    tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    tt = torch.arange(S // bt, dtype=torch.int32, device="cuda")
+    kv = hl_ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, S // bt)
+    hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
+    attn16 = torch.empty((S, cfg.n_head, cfg.head_dim), dtype=torch.float16, device="cuda")
+    hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt, attn16)
+    g = np.random.Generator(np.random.PCG64(5))
+    wo = (g.standard_normal((n_emb, cfg.n_head * cfg.head_dim), dtype=np.float32) / 45).astype(np.float16)
+    got = hl_ctx.linear_f16(attn16.view(S, -1), torch.from_numpy(wo).cuda()).cpu().numpy()
+    ref_attn = oracle_seq(q, k, v, theta=theta, rope_mode=1).reshape(S, -1)
+    want = oracle.matmul(ref_attn, np.ascontiguousarray(wo.astype(np.float32).T))
+    assert float(np.abs(got - want).max()) < 5e-3 and float(np.linalg.norm(got - want) / np.linalg.norm(want)) < 2e-3
+    kv.destroy()
