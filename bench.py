@@ -304,6 +304,67 @@ def extra_config2_pipeline(torch, device_index):
         B.unloadModelBackend()
 
 
+def extra_dense_model(torch, device_index, prefill=2048, decode_steps=64):
+    """The whole dense Llama-3.2-1B layer stack (16 layers, n_emb 2048, n_ffn 8192, vocabulary 128256, 32 / 8 heads of
+    64, fp16 weights, llama3-scaled theta) through the dense backend contract: one prefill, then greedy decode steps.
+    Weights repeat a seeded pool of 4 Mi normals (the kernels do not care; it keeps host set-up short)."""
+    from hippo_leap_b200 import dense as D
+    import hippo_leap_b200 as hl
+
+    L = 16
+    hp = D.DenseHParams(nVocab=128256, nEmb=2048, nLayer=L, nFfn=8192, nHead=32, nHeadKv=8, headDim=64,
+                        ropeFreqBase=500000.0, rmsEps=1e-5, ropeMode=hl.HL_ROPE_SPLIT_HALF, llama3Scaling=True)
+    g = np.random.Generator(np.random.PCG64([5, 77]))
+    pool = g.standard_normal(1 << 22, dtype=np.float32)
+
+    def rep(src, shape):  # src (4 Mi values) repeated to fill shape
+        n = int(np.prod(shape))
+        out = np.empty(-(-n // src.size) * src.size, src.dtype)
+        out.reshape(-1, src.size)[:] = src
+        return out[:n].reshape(shape)
+
+    def mat(*shape):  # scaled 1/sqrt(fan_in)
+        return rep((pool / np.sqrt(shape[-1])).astype(np.float16), shape)
+
+    def gain(*shape):
+        return g.uniform(0.9, 1.1, shape).astype(np.float32)
+
+    E, F, V, qd, kd = hp.nEmb, hp.nFfn, hp.nVocab, hp.nHead * hp.headDim, hp.nHeadKv * hp.headDim
+    w = dict(tok_emb=rep(pool.astype(np.float16), (V, E)), attn_norm=gain(L, E), wq=mat(L, qd, E), wk=mat(L, kd, E),
+             wv=mat(L, kd, E), wo=mat(L, E, qd), q_norm=None, k_norm=None, ffn_norm=gain(L, E), w_gate=mat(L, F, E),
+             w_up=mat(L, F, E), w_down=mat(L, E, F), out_norm=gain(E), w_out=mat(V, E))
+    m = D.DenseModel(hp, w)
+    weight_bytes = sum(v.nbytes for k, v in w.items() if v is not None and k != "tok_emb")
+    cache = D.initKvCache(hp, prefill + decode_steps + 8, device_index)
+    D.loadModelBackend(m, hp, device_index)
+    try:
+        prompt = np.random.Generator(np.random.PCG64([5, 1])).integers(0, hp.nVocab, prefill).astype(np.int32)
+        res = {}
+        for rep in range(2):
+            cache.curLen = 0
+            t0 = time.perf_counter()
+            tok = D.argmaxLast(D.forwardPrefill(m, prompt, cache), hp.nVocab)
+            t1 = time.perf_counter()
+            gpu_ms = 0.0
+            for _ in range(decode_steps):
+                tok, ms = D.forwardDecodeTokenTimed(m, tok, cache)
+                gpu_ms += ms
+            t2 = time.perf_counter()
+            gemm_flops = 2.0 * prefill * L * (E * (qd + 2 * kd) + qd * E + 3 * E * F)
+            res = {"workload": f"Llama-3.2-1B dense model, fp16 weights, prefill {prefill} + {decode_steps} greedy decode "
+                               "steps through the dense backend contract",
+                   "prefill_ms": (t1 - t0) * 1e3, "prefill_tok_per_s": prefill / (t1 - t0),
+                   "prefill_projection_tflops": gemm_flops / (t1 - t0) / 1e12,
+                   "decode_ms_per_token": (t2 - t1) * 1e3 / decode_steps, "decode_tok_per_s": decode_steps / (t2 - t1),
+                   "decode_gpu_ms_per_token": gpu_ms / decode_steps,
+                   "decode_weight_gbs": weight_bytes / (gpu_ms / decode_steps * 1e-3) / 1e9,
+                   "weight_bytes": weight_bytes}
+        return res
+    finally:
+        D.freeKvCache(cache)
+        D.unloadModelBackend()
+
+
 def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     """Config 5 with KV heads split across ranks and one all-gather of the head outputs (fp16)."""
     import hippo_leap_b200 as hl
@@ -377,6 +438,7 @@ def main():
     ap.add_argument("--decode-chunk", type=int, default=0)
     ap.add_argument("--prefill-kernel", type=int, default=0, help="0 auto, 1 warp-MMA, 2 tcgen05, 3 tcgen05 on SM pairs")
     ap.add_argument("--linear-only", action="store_true", help="measure only the dense fp16 projection kernels")
+    ap.add_argument("--dense-only", action="store_true", help="measure only the dense Llama-3.2-1B model")
     ap.add_argument("--pipeline-only", action="store_true", help="measure only the config 2 backend pipeline")
     ap.add_argument("--head-sharded-only", action="store_true",
                     help="measure only the head-sharded config 5 prefill + all-gather at N GPUs")
@@ -410,6 +472,10 @@ def main():
     ctx.set_tuning(args.decode_chunk, args.prefill_kernel)
     if args.linear_only:
         print(json.dumps(extra_linear(ctx, torch, device, peaks)), file=result_out, flush=True)
+        ctx.close()
+        return
+    if args.dense_only:
+        print(json.dumps(extra_dense_model(torch, local_rank)), file=result_out, flush=True)
         ctx.close()
         return
     if args.pipeline_only:
@@ -494,6 +560,7 @@ def main():
             extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False))
             extra["config2_backend_pipeline"] = extra_config2_pipeline(torch, local_rank)
             extra["linear_f16"] = extra_linear(ctx, torch, device, peaks)
+            extra["dense_llama32_1b"] = extra_dense_model(torch, local_rank)
         if cfg.n_head_kv % world == 0:
             extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
                                                                                peaks)

@@ -12,7 +12,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libhl_b200.so")
-SOURCES = ["hl_b200.cu", "backend_host.cu", "standin_backend.cu", "attn_decode_static.cu"]
+SOURCES = ["hl_b200.cu", "backend_host.cu", "standin_backend.cu", "attn_decode_static.cu", "dense_backend.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,367 @@
+// The backend contract on a dense llama / qwen3 model: the whole layer stack of the reference's
+// lkAttentionFfn layers (src/hippo_leap/backends/naive.nim:4054-4086 prefill, 4656-4771 decode) on the
+// GPU.  Per layer:  RMSNorm -> merged Q|K|V projection -> [QK-norm -> RoPE -> KV append -> attention]
+// -> output projection + residual -> RMSNorm -> merged gate|up projection -> SiLU*up -> down projection
+// + residual;  then final norm, vocabulary projection, argmax.  The bracket is the attention hot path
+// (libhl_b200 entry points); the projections are hl_b200_linear_f16; the rest are the row-wise kernels
+// of dense_ops.cuh.  C ABI: include/hl_backend.h (hl_dense_*).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hl_backend.h"
+#include "dense_ops.cuh"
+#include "host_common.h"
+
+namespace {
+
+struct Dense {
+  hl_ctx* ctx = nullptr;
+  int device = -1;
+  bool loaded = false;
+  hl_dense_hparams hp{};
+  // weights on the device
+  __half *tok_emb = nullptr, *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr, *wout = nullptr;
+  float *attn_norm = nullptr, *ffn_norm = nullptr, *out_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+  // activations (capacity in tokens)
+  int cap = 0;
+  float *x = nullptr, *qkv = nullptr, *logits = nullptr;
+  __half *xn = nullptr, *attn = nullptr, *gu = nullptr, *h = nullptr;
+  int32_t *tokens_d = nullptr, *ctx_len_d = nullptr, *table_d = nullptr, *next_d = nullptr;
+  int table_len = 0;
+  int32_t* pinned = nullptr;  // {status code, status detail, next token}
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  std::string err;
+} d;
+
+int32_t dfail(int32_t code, const char* msg) {
+  d.err = msg;
+  return code;
+}
+int32_t dfail_ctx(int32_t code, const char* call) {
+  const char* inner = d.ctx ? hl_b200_last_error(d.ctx) : "";
+  d.err = (inner && *inner) ? std::string(inner) : std::string(call) + " failed";
+  return code;
+}
+#define D_CUDA(expr)                                                         \
+  do {                                                                       \
+    cudaError_t e_ = (expr);                                                 \
+    if (e_ != cudaSuccess) return dfail(HL_ERR_CUDA, cudaGetErrorString(e_)); \
+  } while (0)
+#define D_TRY(expr)                                  \
+  do {                                               \
+    int32_t rc_ = (expr);                            \
+    if (rc_ != HL_OK) return dfail_ctx(rc_, #expr);  \
+  } while (0)
+#define D_PASS(expr)              \
+  do {                            \
+    int32_t rc_ = (expr);         \
+    if (rc_ != HL_OK) return rc_; \
+  } while (0)
+
+int32_t ensure_ctx(int device) {
+  if (d.ctx) return device == d.device ? HL_OK : dfail(HL_ERR_ARG, "dense backend already bound to another device");
+  int32_t rc = hl_b200_create(device, nullptr, &d.ctx);
+  if (rc != HL_OK) return dfail(rc, "hl_b200_create failed: no usable sm_100 device (no CPU fallback exists)");
+  d.device = device;
+  return HL_OK;
+}
+
+int32_t check_hp(const hl_dense_hparams* hp) {
+  if (!hp) return dfail(HL_ERR_ARG, "null hparams");
+  if (hp->n_vocab <= 0 || hp->n_emb <= 0 || hp->n_layer <= 0 || hp->n_ffn <= 0 || hp->n_head <= 0 || hp->n_head_kv <= 0)
+    return dfail(HL_ERR_ARG, "non-positive hparam");
+  if (hp->n_head % hp->n_head_kv != 0) return dfail(HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
+  if (hp->head_dim != 64 && hp->head_dim != 128) return dfail(HL_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+  if ((hp->n_emb & 7) || (hp->n_ffn & 7)) return dfail(HL_ERR_ALIGN, "n_emb and n_ffn must be multiples of 8");
+  return HL_OK;
+}
+
+template <typename T>
+bool upload(T** dst, const void* src, size_t n) {
+  return cudaMalloc(dst, n * sizeof(T)) == cudaSuccess && cudaMemcpy(*dst, src, n * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
+}
+
+int32_t ensure_act(int n) {
+  if (n <= d.cap) return HL_OK;
+  cudaStreamSynchronize(d.ctx->stream);
+  for (float** p : {&d.x, &d.qkv}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  for (__half** p : {&d.xn, &d.attn, &d.gu, &d.h}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  if (d.tokens_d) cudaFree(d.tokens_d);
+  d.tokens_d = nullptr;
+  d.cap = 0;
+  const size_t E = d.hp.n_emb, F = d.hp.n_ffn, qd = static_cast<size_t>(d.hp.n_head) * d.hp.head_dim,
+               kd = static_cast<size_t>(d.hp.n_head_kv) * d.hp.head_dim, N = n;
+  D_CUDA(cudaMalloc(&d.x, N * E * sizeof(float)));
+  D_CUDA(cudaMalloc(&d.qkv, N * (qd + 2 * kd) * sizeof(float)));
+  D_CUDA(cudaMalloc(&d.xn, N * E * sizeof(__half)));
+  D_CUDA(cudaMalloc(&d.attn, N * qd * sizeof(__half)));
+  D_CUDA(cudaMalloc(&d.gu, N * 2 * F * sizeof(__half)));
+  D_CUDA(cudaMalloc(&d.h, N * F * sizeof(__half)));
+  D_CUDA(cudaMalloc(&d.tokens_d, N * sizeof(int32_t)));
+  d.cap = n;
+  return HL_OK;
+}
+
+__global__ void set_i32(int32_t* p, int32_t v) { *p = v; }
+
+// first maximal index wins (src/hippo_leap/sampling.nim:13-19)
+__global__ void argmax_first(const float* __restrict__ logits, int n, int32_t* __restrict__ out) {
+  __shared__ float bv[256];
+  __shared__ int bi[256];
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best || (v == best && i < idx)) {
+      best = v;
+      idx = i;
+    }
+  }
+  bv[threadIdx.x] = best;
+  bi[threadIdx.x] = idx;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = bv[threadIdx.x + s];
+      const int oi = bi[threadIdx.x + s];
+      if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
+        bv[threadIdx.x] = ov;
+        bi[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = bi[0];
+}
+
+int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode) {
+  using namespace hl;
+  hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
+  const hl_dense_hparams& hp = d.hp;
+  const int E = hp.n_emb, F = hp.n_ffn, hd = hp.head_dim, qd = hp.n_head * hd, kd = hp.n_head_kv * hd, qkvd = qd + 2 * kd;
+  D_CUDA(cudaSetDevice(d.device));
+  D_PASS(ensure_act(n));
+  cudaStream_t st = d.ctx->stream;
+  D_CUDA(cudaMemcpyAsync(d.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  if (decode) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
+  embedding_f16_kernel<<<n, 128, 0, st>>>(d.tok_emb, d.tokens_d, E, hp.n_vocab, d.x);
+  d.ctx->launches += 2;
+  for (int l = 0; l < hp.n_layer; ++l) {
+    hl_attn_shape s{};
+    s.n_head = hp.n_head;
+    s.n_head_kv = hp.n_head_kv;
+    s.head_dim = hd;
+    s.rope_dim = hp.rope_dim > 0 ? hp.rope_dim : hd;
+    s.rope_mode = hp.rope_mode;
+    s.rms_eps = hp.rms_eps;
+    s.q_norm_w = d.q_norm ? d.q_norm + static_cast<size_t>(l) * hd : nullptr;
+    s.k_norm_w = d.k_norm ? d.k_norm + static_cast<size_t>(l) * hd : nullptr;
+    rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.attn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
+    d.ctx->launches += 1;
+    D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wqkv + static_cast<size_t>(l) * qkvd * E, E, d.qkv, HL_DTYPE_F32, qkvd,
+                             nullptr, 0, n, qkvd, E, nullptr));
+    hl_view qv{d.qkv, HL_DTYPE_F32, qkvd, hd, 1}, kvw{d.qkv + qd, HL_DTYPE_F32, qkvd, hd, 1},
+        vv{d.qkv + qd + kd, HL_DTYPE_F32, qkvd, hd, 1}, ov{d.attn, HL_DTYPE_F16, qd, hd, 1};
+    if (decode) {
+      D_TRY(hl_b200_kv_append_batch(d.ctx, kv, l, &s, &kvw, &vv, 1, d.ctx_len_d, d.table_d, d.table_len));
+      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, 1, d.ctx_len_d, pos0 + 1, d.table_d, d.table_len, &ov, nullptr));
+    } else {
+      D_TRY(hl_b200_kv_append_seq(d.ctx, kv, l, &s, &kvw, &vv, n, pos0, d.table_d, d.table_len));
+      D_TRY(hl_b200_attn_prefill(d.ctx, kv, l, &s, &qv, n, pos0, d.table_d, d.table_len, &ov, nullptr));
+    }
+    // x += attn . Wo^T   (output projection + residual, naive.nim:4079-4080)
+    D_TRY(hl_b200_linear_f16(d.ctx, d.attn, qd, d.wo + static_cast<size_t>(l) * E * qd, qd, d.x, HL_DTYPE_F32, E, d.x, E, n,
+                             E, qd, nullptr));
+    rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.ffn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
+    D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.gu, HL_DTYPE_F16, 2 * F, nullptr,
+                             0, n, 2 * F, E, nullptr));
+    const int64_t total = static_cast<int64_t>(n) * F;
+    silu_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(d.gu, F, total, d.h);
+    d.ctx->launches += 2;
+    // x += h . Wdown^T   (naive.nim:4085-4086)
+    D_TRY(hl_b200_linear_f16(d.ctx, d.h, F, d.wdown + static_cast<size_t>(l) * E * F, F, d.x, HL_DTYPE_F32, E, d.x, E, n, E, F,
+                             nullptr));
+  }
+  // final norm + vocabulary projection of the LAST position only
+  rmsnorm_rows_kernel<<<1, 256, 0, st>>>(d.x + static_cast<size_t>(n - 1) * E, d.out_norm, E, hp.rms_eps, d.xn);
+  d.ctx->launches += 1;
+  D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wout, E, d.logits, HL_DTYPE_F32, hp.n_vocab, nullptr, 0, 1, hp.n_vocab, E, nullptr));
+  D_CUDA(cudaGetLastError());
+  return HL_OK;
+}
+
+int32_t finish() {
+  D_CUDA(cudaMemcpyAsync(d.pinned, d.ctx->status_d, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_CUDA(cudaStreamSynchronize(d.ctx->stream));
+  if (d.pinned[0] != 0) {
+    const int32_t code = d.pinned[0];
+    cudaMemset(d.ctx->status_d, 0, 2 * sizeof(int32_t));
+    return dfail(code, "a device-side check failed during the forward pass");
+  }
+  return HL_OK;
+}
+
+int32_t check_cache(const hl_kv_cache* cache) {
+  if (!d.loaded) return dfail(HL_ERR_ARG, "no model loaded (loadModelBackend)");
+  if (!cache || !cache->gpu_cache) return dfail(HL_ERR_ARG, "null KV cache (initKvCache)");
+  return HL_OK;
+}
+
+}  // namespace
+
+extern "C" const char* hl_dense_last_error(void) { return d.err.c_str(); }
+
+extern "C" int32_t hl_dense_init_kv_cache(int32_t device, const hl_dense_hparams* hp, int32_t max_len, hl_kv_cache* out) {
+  if (!out) return dfail(HL_ERR_ARG, "null cache");
+  D_PASS(check_hp(hp));
+  if (max_len <= 0) return dfail(HL_ERR_ARG, "max_len must be positive");
+  D_PASS(ensure_ctx(device));
+  const int bt = 128;  // whole 128-key tiles per page: the prefill kernel fetches them as single TMA boxes
+  const int nb = (max_len + bt - 1) / bt;
+  hl_kv* kv = nullptr;
+  D_TRY(hl_b200_kv_create(d.ctx, hp->n_layer, hp->n_head_kv, hp->head_dim, bt, nb, &kv));
+  if (d.table_len < nb) {
+    if (d.table_d) cudaFree(d.table_d);
+    d.table_d = nullptr;
+    std::vector<int32_t> ident(nb);
+    for (int i = 0; i < nb; ++i) ident[i] = i;
+    D_CUDA(cudaMalloc(&d.table_d, nb * sizeof(int32_t)));
+    D_CUDA(cudaMemcpy(d.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice));
+  }
+  d.table_len = nb;
+  out->cur_len = 0;
+  out->max_len = max_len;
+  out->n_head_kv = hp->n_head_kv;
+  out->head_dim = hp->head_dim;
+  out->gpu_cache = kv;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_free_kv_cache(hl_kv_cache* cache) {
+  if (!cache || !cache->gpu_cache || !d.ctx) return dfail(HL_ERR_ARG, "null cache");
+  hl_b200_kv_destroy(d.ctx, static_cast<hl_kv*>(cache->gpu_cache));
+  cache->gpu_cache = nullptr;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_load_model(int32_t device, const hl_dense_hparams* hp, const hl_dense_weights* w) {
+  D_PASS(check_hp(hp));
+  if (!w || !w->tok_emb || !w->attn_norm || !w->wq || !w->wk || !w->wv || !w->wo || !w->ffn_norm || !w->w_gate || !w->w_up ||
+      !w->w_down || !w->out_norm || !w->w_out)
+    return dfail(HL_ERR_ARG, "null weights");
+  if (d.loaded) return dfail(HL_ERR_ARG, "a model is already loaded (one model per process)");
+  D_PASS(ensure_ctx(device));
+  D_CUDA(cudaSetDevice(device));
+  d.hp = *hp;
+  const size_t L = hp->n_layer, E = hp->n_emb, F = hp->n_ffn, V = hp->n_vocab, hd = hp->head_dim;
+  const size_t qd = static_cast<size_t>(hp->n_head) * hd, kd = static_cast<size_t>(hp->n_head_kv) * hd, qkvd = qd + 2 * kd;
+  // merged per-layer matrices: [Wq; Wk; Wv] and [Wgate; Wup], so that each pair of projections is one GEMM
+  std::vector<uint16_t> qkv(L * qkvd * E), gu(L * 2 * F * E);
+  for (size_t l = 0; l < L; ++l) {
+    memcpy(&qkv[l * qkvd * E], w->wq + l * qd * E, qd * E * 2);
+    memcpy(&qkv[l * qkvd * E + qd * E], w->wk + l * kd * E, kd * E * 2);
+    memcpy(&qkv[l * qkvd * E + (qd + kd) * E], w->wv + l * kd * E, kd * E * 2);
+    memcpy(&gu[l * 2 * F * E], w->w_gate + l * F * E, F * E * 2);
+    memcpy(&gu[l * 2 * F * E + F * E], w->w_up + l * F * E, F * E * 2);
+  }
+  bool ok = upload(&d.tok_emb, w->tok_emb, V * E) && upload(&d.wqkv, qkv.data(), qkv.size()) &&
+            upload(&d.wo, w->wo, L * E * qd) && upload(&d.wgu, gu.data(), gu.size()) && upload(&d.wdown, w->w_down, L * E * F) &&
+            upload(&d.wout, w->w_out, V * E) && upload(&d.attn_norm, w->attn_norm, L * E) &&
+            upload(&d.ffn_norm, w->ffn_norm, L * E) && upload(&d.out_norm, w->out_norm, E);
+  if (ok && w->q_norm) ok = upload(&d.q_norm, w->q_norm, L * hd);
+  if (ok && w->k_norm) ok = upload(&d.k_norm, w->k_norm, L * hd);
+  ok = ok && cudaMalloc(&d.logits, V * sizeof(float)) == cudaSuccess && cudaMalloc(&d.ctx_len_d, sizeof(int32_t)) == cudaSuccess &&
+       cudaMalloc(&d.next_d, sizeof(int32_t)) == cudaSuccess && cudaMallocHost(&d.pinned, 4 * sizeof(int32_t)) == cudaSuccess &&
+       cudaEventCreate(&d.e0) == cudaSuccess && cudaEventCreate(&d.e1) == cudaSuccess;
+  d.loaded = true;  // so that unload frees whatever was allocated
+  if (!ok) {
+    cudaGetLastError();
+    hl_dense_unload_model();
+    return dfail(HL_ERR_CUDA, "weight upload failed");
+  }
+  const int rope_dim = hp->rope_dim > 0 ? hp->rope_dim : hp->head_dim;
+  std::vector<float> theta(rope_dim / 2);
+  D_TRY(hl_b200_theta_table_h(hp->rope_freq_base, rope_dim, theta.data()));
+  if (hp->llama3_scaling) D_TRY(hl_b200_theta_llama3_scale_h(theta.data(), rope_dim / 2, 32.f, 1.f, 4.f, 8192));
+  D_TRY(hl_b200_set_rope(d.ctx, theta.data(), rope_dim / 2));
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_unload_model(void) {
+  if (!d.ctx) return HL_OK;
+  cudaSetDevice(d.device);
+  cudaStreamSynchronize(d.ctx->stream);
+  for (__half** p : {&d.tok_emb, &d.wqkv, &d.wo, &d.wgu, &d.wdown, &d.wout, &d.xn, &d.attn, &d.gu, &d.h}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  for (float** p : {&d.attn_norm, &d.ffn_norm, &d.out_norm, &d.q_norm, &d.k_norm, &d.x, &d.qkv, &d.logits}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  for (int32_t** p : {&d.tokens_d, &d.ctx_len_d, &d.table_d, &d.next_d}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  if (d.pinned) cudaFreeHost(d.pinned);
+  d.pinned = nullptr;
+  if (d.e0) cudaEventDestroy(d.e0);
+  if (d.e1) cudaEventDestroy(d.e1);
+  d.e0 = d.e1 = nullptr;
+  d.cap = d.table_len = 0;
+  d.loaded = false;
+  hl_b200_destroy(d.ctx);
+  d.ctx = nullptr;
+  d.device = -1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h) {
+  D_PASS(check_cache(cache));
+  if (!tokens_h || !logits_h) return dfail(HL_ERR_ARG, "null argument");
+  if (n <= 0) return dfail(HL_ERR_ARG, "prefill requires at least one token");
+  if (n > cache->max_len) return dfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
+  D_PASS(forward(tokens_h, n, 0, cache, false));
+  D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_PASS(finish());
+  cache->cur_len = n;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h) {
+  D_PASS(check_cache(cache));
+  if (!logits_h) return dfail(HL_ERR_ARG, "null logits");
+  if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
+  D_PASS(forward(&token, 1, cache->cur_len, cache, true));
+  D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_PASS(finish());
+  cache->cur_len += 1;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token, float* gpu_ms) {
+  D_PASS(check_cache(cache));
+  if (!next_token) return dfail(HL_ERR_ARG, "null next_token");
+  if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, d.ctx->stream));
+  D_PASS(forward(&token, 1, cache->cur_len, cache, true));
+  argmax_first<<<1, 256, 0, d.ctx->stream>>>(d.logits, d.hp.n_vocab, d.next_d);
+  d.ctx->launches += 1;
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, d.ctx->stream));
+  D_CUDA(cudaMemcpyAsync(&d.pinned[2], d.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_PASS(finish());
+  if (gpu_ms) D_CUDA(cudaEventElapsedTime(gpu_ms, d.e0, d.e1));
+  *next_token = d.pinned[2];
+  cache->cur_len += 1;
+  return HL_OK;
+}

@@ -1,0 +1,56 @@
+// The small row-wise operators of a dense llama / qwen3 layer around the attention path
+// (src/hippo_leap/backends/naive.nim): embedding lookup (:2976-3001), RMSNorm over the embedding
+// dimension (rmsnormColsKernel :2802-2842), SiLU(gate) * up (siluMulKernel :2179-2197).  Activations are
+// token-major here ([n_tok][dim]); the residual stream stays fp32, GEMM inputs are written as fp16.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace hl {
+
+// x[t][:] = float(table[token[t]][:])
+__global__ void embedding_f16_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, int n_emb,
+                                     int n_vocab, float* __restrict__ x) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
+  const __half2* src = reinterpret_cast<const __half2*>(table + static_cast<int64_t>(tok) * n_emb);
+  float2* dst = reinterpret_cast<float2*>(x + static_cast<int64_t>(t) * n_emb);
+  for (int i = threadIdx.x; i < n_emb / 2; i += blockDim.x) dst[i] = __half22float2(src[i]);
+}
+
+// out[t][:] = fp16( x[t][:] * (1 / sqrt(mean(x[t]^2) + eps)) * w[:] ); one block per token row
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           int dim, float eps, __half* __restrict__ out) {
+  __shared__ float red[8];
+  __shared__ float inv_s;
+  const float* xr = x + static_cast<int64_t>(blockIdx.x) * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += 256) ss += xr[i] * xr[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    inv_s = 1.0f / sqrtf(tot / static_cast<float>(dim) + eps);
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  __half* orow = out + static_cast<int64_t>(blockIdx.x) * dim;
+  for (int i = threadIdx.x; i < dim; i += 256) orow[i] = __float2half_rn(xr[i] * inv * w[i]);
+}
+
+// h[t][f] = fp16( silu(gate) * up ), gate = gu[t][f], up = gu[t][n_ffn + f]  (one merged gate|up GEMM output, fp16)
+__global__ void silu_mul_kernel(const __half* __restrict__ gu, int n_ffn, int64_t total, __half* __restrict__ h) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t t = idx / n_ffn, f = idx % n_ffn;
+  const float g = __half2float(gu[t * 2 * n_ffn + f]);
+  const float u = __half2float(gu[t * 2 * n_ffn + n_ffn + f]);
+  const float sig = 1.0f / (1.0f + expf(-g));
+  h[idx] = __float2half_rn(g * sig * u);
+}
+
+}  // namespace hl

@@ -81,6 +81,48 @@ const char* hl_backend_last_error(void);
 /* Kernel launches issued by the backend's context so far. */
 int64_t hl_backend_launch_count(void);
 
+/* ---- the same contract on a DENSE llama / qwen3 model ------------------------------------------
+ * The first step beyond the hot path: the layers either side of attention for the reference's
+ * lkAttentionFfn layer kind (naive.nim:4054-4086, 4656-4771) with dense fp16 weights -- embedding,
+ * RMSNorm, Q/K/V and output projections, SwiGLU FFN, final norm, vocabulary projection, argmax -- so
+ * that forwardPrefill / forwardDecode run a whole model forward on the GPU.  Weights are plain host
+ * arrays (row-major [out][in] fp16 matrices, fp32 norm vectors): there is no GGUF reader and none of the
+ * reference's quantised formats here. */
+typedef struct hl_dense_hparams {
+  int32_t n_vocab, n_emb, n_layer, n_ffn, n_head, n_head_kv, head_dim, rope_dim;
+  float rope_freq_base, rms_eps;
+  int32_t rope_mode, llama3_scaling;
+} hl_dense_hparams;
+
+typedef struct hl_dense_weights {
+  const uint16_t* tok_emb;   /* [n_vocab][n_emb] fp16                            token_embd.weight   */
+  const float* attn_norm;    /* [n_layer][n_emb]                                 blk.N.attn_norm     */
+  const uint16_t* wq;        /* [n_layer][n_head*head_dim][n_emb]                blk.N.attn_q        */
+  const uint16_t* wk;        /* [n_layer][n_head_kv*head_dim][n_emb]             blk.N.attn_k        */
+  const uint16_t* wv;        /* [n_layer][n_head_kv*head_dim][n_emb]             blk.N.attn_v        */
+  const uint16_t* wo;        /* [n_layer][n_emb][n_head*head_dim]                blk.N.attn_output   */
+  const float* q_norm;       /* [n_layer][head_dim] or NULL                      blk.N.attn_q_norm   */
+  const float* k_norm;       /* [n_layer][head_dim] or NULL                      blk.N.attn_k_norm   */
+  const float* ffn_norm;     /* [n_layer][n_emb]                                 blk.N.ffn_norm      */
+  const uint16_t* w_gate;    /* [n_layer][n_ffn][n_emb]                          blk.N.ffn_gate      */
+  const uint16_t* w_up;      /* [n_layer][n_ffn][n_emb]                          blk.N.ffn_up        */
+  const uint16_t* w_down;    /* [n_layer][n_emb][n_ffn]                          blk.N.ffn_down      */
+  const float* out_norm;     /* [n_emb]                                          output_norm         */
+  const uint16_t* w_out;     /* [n_vocab][n_emb]                                 output              */
+} hl_dense_weights;
+
+int32_t hl_dense_init_kv_cache(int32_t device, const hl_dense_hparams* hp, int32_t max_len, hl_kv_cache* out);
+int32_t hl_dense_free_kv_cache(hl_kv_cache* cache);
+int32_t hl_dense_load_model(int32_t device, const hl_dense_hparams* hp, const hl_dense_weights* w);
+int32_t hl_dense_unload_model(void);
+/* forwardPrefill: logits of the last position [n_vocab]; starts at position 0, sets cur_len = n. */
+int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
+/* forwardDecode: one token at position cache.cur_len; "KV cache full" at capacity. */
+int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
+/* forwardDecodeTokenTimed: argmax on the device, optional device time of the step. */
+int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token, float* gpu_ms);
+const char* hl_dense_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,7 +23,7 @@ def _header_text():
 
 
 def test_library_exports_every_declared_symbol():
-    declared = set(re.findall(r"\b(hl_(?:b200|backend)_\w+)\s*\(", _header_text()))
+    declared = set(re.findall(r"\b(hl_(?:b200|backend|dense)_\w+)\s*\(", _header_text()))
     assert len(declared) >= 18
     lib = C.CDLL(_lib.LIB_PATH)
     missing = [s for s in sorted(declared) if not hasattr(lib, s)]
@@ -34,10 +34,14 @@ def test_binding_table_covers_the_header():
     from hippo_leap_b200 import backend
     declared = set(re.findall(r"\b(hl_b200_\w+)\s*\(", _header_text()))
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    from hippo_leap_b200 import dense
     declared_b = set(re.findall(r"\b(hl_backend_\w+)\s*\(", _header_text()))
     assert declared_b == set(backend.BACKEND_SYMBOLS), declared_b ^ set(backend.BACKEND_SYMBOLS)
+    declared_d = set(re.findall(r"\b(hl_dense_\w+)\s*\(", _header_text()))
+    assert declared_d == set(dense.DENSE_SYMBOLS), declared_d ^ set(dense.DENSE_SYMBOLS)
     _lib.load()
     backend._lib()
+    dense._lib()
 
 
 def test_status_and_enum_values_match_header():

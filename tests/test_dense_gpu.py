@@ -1,0 +1,133 @@
+"""The backend contract on a dense llama / qwen3 model (hl_dense_*): embedding, RMSNorm, Q/K/V/O projections,
+SwiGLU FFN and vocabulary projection around the attention path, against the same layer stack written with
+the oracle's tensor ops (matmul, rmsnorm, attention) -- the lkAttentionFfn branch of the reference's forward
+pass (src/hippo_leap/backends/naive.nim:4054-4086).  Two oracles: plain float32 (loose tolerance: the CUDA path
+feeds its GEMMs fp16 activations) and one that rounds activations to fp16 at the same points (tight)."""
+import numpy as np
+import pytest
+
+import hippo_leap_b200 as hl
+import oracle
+from hippo_leap_b200 import dense as D
+from tests.helpers import assert_parity, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+class OracleDense:
+    def __init__(self, m: D.DenseModel, max_len: int, mirror_fp16: bool):
+        hp = m.hparams
+        self.m, self.hp, self.mirror = m, hp, mirror_fp16
+        th = oracle.theta_table(hp.ropeDim or hp.headDim, hp.ropeFreqBase)
+        self.theta = hl.theta_llama3_scale(th) if hp.llama3Scaling else th
+        self.caches = [oracle.SeqCache(max_len, hp.nHeadKv, hp.headDim) for _ in range(hp.nLayer)]
+        self.t = {k: np.ascontiguousarray(np.swapaxes(m.w[k].astype(np.float32), -1, -2))
+                  for k in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down", "w_out")}
+
+    def r(self, a):
+        return oracle.round_fp16(a) if self.mirror else a
+
+    def forward(self, tokens):
+        hp, w, t = self.hp, self.m.w, self.t
+        toks = np.asarray(tokens, np.int64)
+        n = len(toks)
+        x = w["tok_emb"][toks].astype(np.float32)
+        for l in range(hp.nLayer):
+            xn = self.r(oracle.rmsnorm(x, w["attn_norm"][l], hp.rmsEps))
+            q = oracle.matmul(xn, t["wq"][l]).reshape(n, hp.nHead, hp.headDim)
+            k = oracle.matmul(xn, t["wk"][l]).reshape(n, hp.nHeadKv, hp.headDim)
+            v = oracle.matmul(xn, t["wv"][l]).reshape(n, hp.nHeadKv, hp.headDim)
+            o = oracle.attn_forward(q, k, v, self.caches[l], theta=self.theta, rope_mode=hp.ropeMode,
+                                    q_norm_w=None if w["q_norm"] is None else w["q_norm"][l],
+                                    k_norm_w=None if w["k_norm"] is None else w["k_norm"][l], eps=hp.rmsEps,
+                                    kv_fp16=self.mirror)
+            o = self.r(o.reshape(n, -1))
+            x = (x + oracle.matmul(o, t["wo"][l])).astype(np.float32)
+            xn = self.r(oracle.rmsnorm(x, w["ffn_norm"][l], hp.rmsEps))
+            g = self.r(oracle.matmul(xn, t["w_gate"][l]))
+            u = self.r(oracle.matmul(xn, t["w_up"][l]))
+            h = self.r((g / (1.0 + np.exp(-g))).astype(np.float32) * u)  # silu(x) = x / (1 + exp(-x)), tensor.nim silu
+            x = (x + oracle.matmul(h, t["w_down"][l])).astype(np.float32)
+        xn = self.r(oracle.rmsnorm(x[-1:], w["out_norm"], hp.rmsEps))
+        return oracle.matmul(xn, t["w_out"])
+
+
+CASES = {
+    "llama_hd64": (D.DenseHParams(nVocab=512, nEmb=256, nLayer=2, nFfn=512, nHead=4, nHeadKv=2, headDim=64,
+                                  ropeFreqBase=10000.0, rmsEps=1e-5, ropeMode=hl.HL_ROPE_SPLIT_HALF), False),
+    "llama3_interleaved": (D.DenseHParams(nVocab=384, nEmb=256, nLayer=2, nFfn=768, nHead=4, nHeadKv=4, headDim=64,
+                                          ropeFreqBase=500000.0, rmsEps=1e-5, ropeMode=hl.HL_ROPE_INTERLEAVED,
+                                          llama3Scaling=True), False),
+    "qwen3_hd128_qknorm": (D.DenseHParams(nVocab=640, nEmb=512, nLayer=3, nFfn=1024, nHead=4, nHeadKv=1, headDim=128,
+                                          ropeFreqBase=1000000.0, rmsEps=1e-6, ropeMode=hl.HL_ROPE_SPLIT_HALF), True),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("prompt_len", [5, 150])
+def test_dense_model_against_oracle(name, prompt_len):
+    hp, qk_norm = CASES[name]
+    steps, seed = 6, 11
+    m = D.random_dense_model(hp, seed, qk_norm)
+    max_len = prompt_len + steps + 2
+    cache = D.initKvCache(hp, max_len)
+    D.loadModelBackend(m, hp)
+    plain, mirror = OracleDense(m, max_len, False), OracleDense(m, max_len, True)
+    try:
+        prompt = np.random.Generator(np.random.PCG64([seed, 1])).integers(0, hp.nVocab, prompt_len).astype(np.int32)
+        cache.curLen = 0
+        logits = D.forwardPrefill(m, prompt, cache)
+        assert cache.curLen == prompt_len
+        feed = prompt
+        for step in range(steps + 1):
+            # each step: both oracles and the CUDA path consume the same tokens (the oracle's greedy choice), so one
+            # near-tie cannot end the comparison early; the argmax must agree wherever the margin is clear
+            want, want_m = plain.forward(feed), mirror.forward(feed)
+            scale = float(np.abs(want).max())
+            top2 = np.sort(want_m[0])[-2:]
+            clear = top2[1] - top2[0] > 1e-2 * scale
+            tok = D.argmaxLast(want_m, hp.nVocab)
+            if logits is not None:
+                assert_parity(logits, want, f"step {step} logits vs float32 oracle", max_abs_tol=1e-2 * scale,
+                              rel_l2_tol=5e-3)
+                assert_parity(logits, want_m, f"step {step} logits vs fp16-activation oracle", max_abs_tol=3e-3 * scale,
+                              rel_l2_tol=1.5e-3)
+                got_tok = D.argmaxLast(logits, hp.nVocab)
+            assert got_tok == tok or not clear, f"step {step}: token {got_tok}, oracle {tok}"
+            if step == steps:
+                break
+            feed = [tok]
+            if step % 2 == 0:
+                logits = D.forwardDecode(m, tok, cache)
+            else:
+                logits = None
+                got_tok, ms = D.forwardDecodeTokenTimed(m, tok, cache)
+                assert ms > 0
+            assert cache.curLen == prompt_len + step + 1
+        assert cache.curLen <= max_len
+    finally:
+        D.unloadModelBackend()
+
+
+def test_dense_contract_errors():
+    hp, _ = CASES["llama_hd64"]
+    m = D.random_dense_model(hp, 3)
+    with pytest.raises(ValueError, match="no model loaded"):
+        D.forwardDecode(m, 1, D.KvCache())
+    cache = D.initKvCache(hp, 8)
+    D.loadModelBackend(m, hp)
+    try:
+        with pytest.raises(ValueError, match="already loaded"):
+            D.loadModelBackend(m, hp)
+        with pytest.raises(ValueError, match="exceeds KV cache capacity"):
+            D.forwardPrefill(m, np.zeros(9, np.int32), cache)
+        with pytest.raises(ValueError, match="at least one token"):
+            D.forwardPrefill(m, np.zeros(0, np.int32), cache)
+        D.forwardPrefill(m, np.arange(8, dtype=np.int32), cache)
+        with pytest.raises(ValueError, match="KV cache full"):
+            D.forwardDecode(m, 1, cache)
+    finally:
+        D.unloadModelBackend()
+    bad = D.DenseHParams(nVocab=64, nEmb=64, nLayer=1, nFfn=64, nHead=3, nHeadKv=2, headDim=64)
+    with pytest.raises(ValueError, match="divisible"):
+        D.initKvCache(bad, 8)
