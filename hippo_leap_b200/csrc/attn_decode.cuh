@@ -295,6 +295,9 @@ __global__ void __launch_bounds__((NW + 1) * 32)
 // Second pass of split-KV: merge the chunk partials of one (sequence, head).
 template <int HD>
 __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
+  // a kernel queued behind this one with programmatic stream serialisation (the output projection's GEMV) may start
+  // its weight prefetch now; it still waits for this grid to finish before it reads the attention output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int ctx = a.ctx_lens[b];
   const int n = (ctx + a.chunk_tokens - 1) / a.chunk_tokens;

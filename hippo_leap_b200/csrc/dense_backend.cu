@@ -30,10 +30,17 @@ struct Dense {
   int cap = 0;
   float *x = nullptr, *qkv = nullptr, *logits = nullptr;
   __half *xn = nullptr, *attn = nullptr, *gu = nullptr, *h = nullptr;
-  int32_t *tokens_d = nullptr, *ctx_len_d = nullptr, *table_d = nullptr, *next_d = nullptr;
+  int32_t *tokens_d = nullptr, *ctx_len_d = nullptr, *table_d = nullptr, *next_d = nullptr, *cand_i = nullptr;
+  float* cand_v = nullptr;
   int table_len = 0;
-  int32_t* pinned = nullptr;  // {status code, status detail, next token}
+  int32_t* pinned = nullptr;  // [0..1] device status, [2] next token, [4] token id of the step, [5] its context length
   cudaEvent_t e0 = nullptr, e1 = nullptr;
+  // one decode step captured as a CUDA graph, replayed per token (fed by pinned[4..5] through copy nodes)
+  bool use_graph = true;
+  cudaGraphExec_t graph = nullptr;
+  void* graph_kv = nullptr;
+  int graph_max_len = 0;
+  int64_t graph_kernels = 0;  // kernels inside one replay
   std::string err;
 } d;
 
@@ -114,37 +121,64 @@ int32_t ensure_act(int n) {
 
 __global__ void set_i32(int32_t* p, int32_t v) { *p = v; }
 
-// first maximal index wins (src/hippo_leap/sampling.nim:13-19)
-__global__ void argmax_first(const float* __restrict__ logits, int n, int32_t* __restrict__ out) {
-  __shared__ float bv[256];
-  __shared__ int bi[256];
-  float best = -INFINITY;
-  int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = logits[i];
-    if (v > best || (v == best && i < idx)) {
-      best = v;
-      idx = i;
-    }
+// argmax over the vocabulary, first maximal index wins (src/hippo_leap/sampling.nim:13-19), in two launches:
+// kArgmaxBlocks blocks each reduce a contiguous range to one (value, index) candidate, one block reduces those.
+constexpr int kArgmaxBlocks = 128;
+
+__device__ __forceinline__ void argmax_take(float& best, int& idx, float v, int i) {
+  if (v > best || (v == best && i < idx)) {
+    best = v;
+    idx = i;
   }
-  bv[threadIdx.x] = best;
-  bi[threadIdx.x] = idx;
-  __syncthreads();
-  for (int s = 128; s > 0; s >>= 1) {
-    if (threadIdx.x < s) {
-      const float ov = bv[threadIdx.x + s];
-      const int oi = bi[threadIdx.x + s];
-      if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
-        bv[threadIdx.x] = ov;
-        bi[threadIdx.x] = oi;
-      }
-    }
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) *out = bi[0];
 }
 
-int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode) {
+__device__ __forceinline__ void argmax_block_reduce(float& best, int& idx) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    argmax_take(best, idx, ov, oi);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    bv[threadIdx.x >> 5] = best;
+    bi[threadIdx.x >> 5] = idx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) argmax_take(best, idx, bv[w], bi[w]);
+}
+
+__global__ void __launch_bounds__(256) argmax_partial(const float* __restrict__ logits, int n, float* __restrict__ cand_v,
+                                                      int32_t* __restrict__ cand_i) {
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int beg = blockIdx.x * per, end = min(n, beg + per);
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = beg + threadIdx.x; i < end; i += 256) argmax_take(best, idx, logits[i], i);
+  argmax_block_reduce(best, idx);
+  if (threadIdx.x == 0) {
+    cand_v[blockIdx.x] = best;
+    cand_i[blockIdx.x] = idx;
+  }
+}
+
+__global__ void __launch_bounds__(kArgmaxBlocks) argmax_final(const float* __restrict__ cand_v,
+                                                              const int32_t* __restrict__ cand_i, int32_t* __restrict__ out) {
+  float best = cand_v[threadIdx.x];
+  int idx = cand_i[threadIdx.x];
+  argmax_block_reduce(best, idx);
+  if (threadIdx.x == 0) *out = idx == 0x7fffffff ? 0 : idx;
+}
+
+void launch_argmax(cudaStream_t st);
+
+// One forward over n tokens starting at position pos0; decode is n == 1.  `grid_ctx` sizes the decode grid and its
+// scratch (>= the real context); with `from_pinned` the token id and the context length come from the pinned step
+// record through copy nodes, so that a captured graph of the sequence can be replayed for every token.
+int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode, int grid_ctx = 0,
+                bool from_pinned = false) {
   using namespace hl;
   hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
   const hl_dense_hparams& hp = d.hp;
@@ -152,8 +186,15 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
   D_CUDA(cudaSetDevice(d.device));
   D_PASS(ensure_act(n));
   cudaStream_t st = d.ctx->stream;
-  D_CUDA(cudaMemcpyAsync(d.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  if (decode) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
+  if (from_pinned) {
+    D_CUDA(cudaMemcpyAsync(d.tokens_d, &d.pinned[4], sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    D_CUDA(cudaMemcpyAsync(d.ctx_len_d, &d.pinned[5], sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  } else {
+    D_CUDA(cudaMemcpyAsync(d.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    if (decode) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
+  }
+  if (grid_ctx < pos0 + 1) grid_ctx = pos0 + 1;
+  const bool fused = n <= 4;  // decode-sized: RMSNorm and SwiGLU run as prologues of the projection that follows them
   embedding_f16_kernel<<<n, 128, 0, st>>>(d.tok_emb, d.tokens_d, E, hp.n_vocab, d.x);
   d.ctx->launches += 2;
   for (int l = 0; l < hp.n_layer; ++l) {
@@ -166,15 +207,21 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     s.rms_eps = hp.rms_eps;
     s.q_norm_w = d.q_norm ? d.q_norm + static_cast<size_t>(l) * hd : nullptr;
     s.k_norm_w = d.k_norm ? d.k_norm + static_cast<size_t>(l) * hd : nullptr;
-    rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.attn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
-    d.ctx->launches += 1;
-    D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wqkv + static_cast<size_t>(l) * qkvd * E, E, d.qkv, HL_DTYPE_F32, qkvd,
-                             nullptr, 0, n, qkvd, E, nullptr));
+    if (fused) {
+      D_TRY(hl_linear_decode_fused(d.ctx, 1, 0, d.x, E, d.attn_norm + static_cast<size_t>(l) * E, hp.rms_eps,
+                                   d.wqkv + static_cast<size_t>(l) * qkvd * E, E, d.qkv, HL_DTYPE_F32, qkvd, nullptr, 0, n,
+                                   qkvd, E));
+    } else {
+      rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.attn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
+      d.ctx->launches += 1;
+      D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wqkv + static_cast<size_t>(l) * qkvd * E, E, d.qkv, HL_DTYPE_F32, qkvd,
+                               nullptr, 0, n, qkvd, E, nullptr));
+    }
     hl_view qv{d.qkv, HL_DTYPE_F32, qkvd, hd, 1}, kvw{d.qkv + qd, HL_DTYPE_F32, qkvd, hd, 1},
         vv{d.qkv + qd + kd, HL_DTYPE_F32, qkvd, hd, 1}, ov{d.attn, HL_DTYPE_F16, qd, hd, 1};
     if (decode) {
       D_TRY(hl_b200_kv_append_batch(d.ctx, kv, l, &s, &kvw, &vv, 1, d.ctx_len_d, d.table_d, d.table_len));
-      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, 1, d.ctx_len_d, pos0 + 1, d.table_d, d.table_len, &ov, nullptr));
+      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, 1, d.ctx_len_d, grid_ctx, d.table_d, d.table_len, &ov, nullptr));
     } else {
       D_TRY(hl_b200_kv_append_seq(d.ctx, kv, l, &s, &kvw, &vv, n, pos0, d.table_d, d.table_len));
       D_TRY(hl_b200_attn_prefill(d.ctx, kv, l, &s, &qv, n, pos0, d.table_d, d.table_len, &ov, nullptr));
@@ -182,22 +229,35 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     // x += attn . Wo^T   (output projection + residual, naive.nim:4079-4080)
     D_TRY(hl_b200_linear_f16(d.ctx, d.attn, qd, d.wo + static_cast<size_t>(l) * E * qd, qd, d.x, HL_DTYPE_F32, E, d.x, E, n,
                              E, qd, nullptr));
-    rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.ffn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
-    D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.gu, HL_DTYPE_F16, 2 * F, nullptr,
-                             0, n, 2 * F, E, nullptr));
-    const int64_t total = static_cast<int64_t>(n) * F;
-    silu_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(d.gu, F, total, d.h);
-    d.ctx->launches += 2;
-    // x += h . Wdown^T   (naive.nim:4085-4086)
-    D_TRY(hl_b200_linear_f16(d.ctx, d.h, F, d.wdown + static_cast<size_t>(l) * E * F, F, d.x, HL_DTYPE_F32, E, d.x, E, n, E, F,
-                             nullptr));
+    if (fused) {
+      // h = silu(gate) * up in the epilogue of the merged projection; x += h . Wdown^T   (naive.nim:4083-4086)
+      D_TRY(hl_linear_decode_fused(d.ctx, 1, 1, d.x, E, d.ffn_norm + static_cast<size_t>(l) * E, hp.rms_eps,
+                                   d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.h, HL_DTYPE_F16, F, nullptr, 0, n, 2 * F, E));
+      D_TRY(hl_linear_decode_fused(d.ctx, 0, 0, d.h, F, nullptr, 0.f, d.wdown + static_cast<size_t>(l) * E * F, F, d.x,
+                                   HL_DTYPE_F32, E, d.x, E, n, E, F));
+    } else {
+      rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.ffn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
+      D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.gu, HL_DTYPE_F16, 2 * F,
+                               nullptr, 0, n, 2 * F, E, nullptr));
+      const int64_t total = static_cast<int64_t>(n) * F;
+      silu_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(d.gu, F, total, d.h);
+      d.ctx->launches += 2;
+      // x += h . Wdown^T   (naive.nim:4085-4086)
+      D_TRY(hl_b200_linear_f16(d.ctx, d.h, F, d.wdown + static_cast<size_t>(l) * E * F, F, d.x, HL_DTYPE_F32, E, d.x, E, n, E,
+                               F, nullptr));
+    }
   }
   // final norm + vocabulary projection of the LAST position only
-  rmsnorm_rows_kernel<<<1, 256, 0, st>>>(d.x + static_cast<size_t>(n - 1) * E, d.out_norm, E, hp.rms_eps, d.xn);
-  d.ctx->launches += 1;
-  D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wout, E, d.logits, HL_DTYPE_F32, hp.n_vocab, nullptr, 0, 1, hp.n_vocab, E, nullptr));
+  D_TRY(hl_linear_decode_fused(d.ctx, 1, 0, d.x + static_cast<size_t>(n - 1) * E, E, d.out_norm, hp.rms_eps, d.wout, E, d.logits,
+                               HL_DTYPE_F32, hp.n_vocab, nullptr, 0, 1, hp.n_vocab, E));
   D_CUDA(cudaGetLastError());
   return HL_OK;
+}
+
+void launch_argmax(cudaStream_t st) {
+  argmax_partial<<<kArgmaxBlocks, 256, 0, st>>>(d.logits, d.hp.n_vocab, d.cand_v, d.cand_i);
+  argmax_final<<<1, kArgmaxBlocks, 0, st>>>(d.cand_v, d.cand_i, d.next_d);
+  d.ctx->launches += 2;
 }
 
 int32_t finish() {
@@ -217,7 +277,74 @@ int32_t check_cache(const hl_kv_cache* cache) {
   return HL_OK;
 }
 
+// Capture one decode step (every layer, logits, argmax, result and status copies) into a CUDA graph.  The decode grid
+// and the split-KV scratch are sized for the cache's capacity, so one graph serves every position.
+int32_t ensure_decode_graph(hl_kv_cache* cache) {
+  if (d.graph && d.graph_kv == cache->gpu_cache && d.graph_max_len == cache->max_len) return HL_OK;
+  if (d.graph) cudaGraphExecDestroy(d.graph);
+  d.graph = nullptr;
+  cudaStream_t st = d.ctx->stream;
+  // an uncaptured pass first: it configures kernels and grows every scratch buffer, so nothing allocates or
+  // synchronises during capture; the first replay repeats it at the same position with the same values
+  D_PASS(forward(nullptr, 1, d.pinned[5] - 1, cache, true, cache->max_len, true));
+  D_CUDA(cudaStreamSynchronize(st));
+  D_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  const int64_t counted = d.ctx->launches;
+  int32_t rc = forward(nullptr, 1, d.pinned[5] - 1, cache, true, cache->max_len, true);
+  if (rc == HL_OK) {
+    launch_argmax(st);
+    cudaMemcpyAsync(&d.pinned[2], d.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    cudaMemcpyAsync(d.pinned, d.ctx->status_d, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  }
+  d.graph_kernels = d.ctx->launches - counted;
+  d.ctx->launches = counted;  // recorded, not launched
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(st, &graph);
+  if (rc != HL_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess || !graph) return dfail(HL_ERR_CUDA, "stream capture of the decode step failed");
+  e = cudaGraphInstantiate(&d.graph, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return dfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
+  d.graph_kv = cache->gpu_cache;
+  d.graph_max_len = cache->max_len;
+  return HL_OK;
+}
+
+// One decode step by graph replay; logits_h (optional) receives the logits, next_token (optional) the argmax.
+int32_t decode_graph(int32_t token, hl_kv_cache* cache, float* logits_h, int32_t* next_token, float* gpu_ms) {
+  if (cache->cur_len < 0) return dfail(HL_ERR_ARG, "negative cur_len");
+  D_CUDA(cudaSetDevice(d.device));
+  d.pinned[4] = token;
+  d.pinned[5] = cache->cur_len + 1;
+  D_PASS(ensure_decode_graph(cache));
+  cudaStream_t st = d.ctx->stream;
+  const int64_t before = d.ctx->launches;
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
+  D_CUDA(cudaGraphLaunch(d.graph, st));
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, st));
+  if (logits_h) D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, st));
+  D_CUDA(cudaStreamSynchronize(st));
+  d.ctx->launches = before + d.graph_kernels;
+  if (d.pinned[0] != 0) {
+    const int32_t code = d.pinned[0];
+    cudaMemset(d.ctx->status_d, 0, 2 * sizeof(int32_t));
+    return dfail(code, "a device-side check failed during the decode step");
+  }
+  if (gpu_ms) D_CUDA(cudaEventElapsedTime(gpu_ms, d.e0, d.e1));
+  if (next_token) *next_token = d.pinned[2];
+  cache->cur_len += 1;
+  return HL_OK;
+}
+
 }  // namespace
+
+extern "C" int32_t hl_dense_set_decode_graph(int32_t enabled) {
+  d.use_graph = enabled != 0;
+  return HL_OK;
+}
 
 extern "C" const char* hl_dense_last_error(void) { return d.err.c_str(); }
 
@@ -249,6 +376,11 @@ extern "C" int32_t hl_dense_init_kv_cache(int32_t device, const hl_dense_hparams
 
 extern "C" int32_t hl_dense_free_kv_cache(hl_kv_cache* cache) {
   if (!cache || !cache->gpu_cache || !d.ctx) return dfail(HL_ERR_ARG, "null cache");
+  if (d.graph && d.graph_kv == cache->gpu_cache) {
+    cudaGraphExecDestroy(d.graph);
+    d.graph = nullptr;
+    d.graph_kv = nullptr;
+  }
   hl_b200_kv_destroy(d.ctx, static_cast<hl_kv*>(cache->gpu_cache));
   cache->gpu_cache = nullptr;
   return HL_OK;
@@ -265,14 +397,17 @@ extern "C" int32_t hl_dense_load_model(int32_t device, const hl_dense_hparams* h
   d.hp = *hp;
   const size_t L = hp->n_layer, E = hp->n_emb, F = hp->n_ffn, V = hp->n_vocab, hd = hp->head_dim;
   const size_t qd = static_cast<size_t>(hp->n_head) * hd, kd = static_cast<size_t>(hp->n_head_kv) * hd, qkvd = qd + 2 * kd;
-  // merged per-layer matrices: [Wq; Wk; Wv] and [Wgate; Wup], so that each pair of projections is one GEMM
+  // merged per-layer matrices: [Wq; Wk; Wv], and Wgate / Wup interleaved row by row, so that each group of
+  // projections is one GEMM and SiLU(gate) * up can run in the epilogue of the decode projection
   std::vector<uint16_t> qkv(L * qkvd * E), gu(L * 2 * F * E);
   for (size_t l = 0; l < L; ++l) {
     memcpy(&qkv[l * qkvd * E], w->wq + l * qd * E, qd * E * 2);
     memcpy(&qkv[l * qkvd * E + qd * E], w->wk + l * kd * E, kd * E * 2);
     memcpy(&qkv[l * qkvd * E + (qd + kd) * E], w->wv + l * kd * E, kd * E * 2);
-    memcpy(&gu[l * 2 * F * E], w->w_gate + l * F * E, F * E * 2);
-    memcpy(&gu[l * 2 * F * E + F * E], w->w_up + l * F * E, F * E * 2);
+    for (size_t f = 0; f < F; ++f) {  // rows interleaved: 2f = gate_f, 2f + 1 = up_f
+      memcpy(&gu[(l * 2 * F + 2 * f) * E], w->w_gate + (l * F + f) * E, E * 2);
+      memcpy(&gu[(l * 2 * F + 2 * f + 1) * E], w->w_up + (l * F + f) * E, E * 2);
+    }
   }
   bool ok = upload(&d.tok_emb, w->tok_emb, V * E) && upload(&d.wqkv, qkv.data(), qkv.size()) &&
             upload(&d.wo, w->wo, L * E * qd) && upload(&d.wgu, gu.data(), gu.size()) && upload(&d.wdown, w->w_down, L * E * F) &&
@@ -281,7 +416,8 @@ extern "C" int32_t hl_dense_load_model(int32_t device, const hl_dense_hparams* h
   if (ok && w->q_norm) ok = upload(&d.q_norm, w->q_norm, L * hd);
   if (ok && w->k_norm) ok = upload(&d.k_norm, w->k_norm, L * hd);
   ok = ok && cudaMalloc(&d.logits, V * sizeof(float)) == cudaSuccess && cudaMalloc(&d.ctx_len_d, sizeof(int32_t)) == cudaSuccess &&
-       cudaMalloc(&d.next_d, sizeof(int32_t)) == cudaSuccess && cudaMallocHost(&d.pinned, 4 * sizeof(int32_t)) == cudaSuccess &&
+       cudaMalloc(&d.next_d, sizeof(int32_t)) == cudaSuccess && cudaMalloc(&d.cand_v, kArgmaxBlocks * sizeof(float)) == cudaSuccess &&
+       cudaMalloc(&d.cand_i, kArgmaxBlocks * sizeof(int32_t)) == cudaSuccess && cudaMallocHost(&d.pinned, 8 * sizeof(int32_t)) == cudaSuccess &&
        cudaEventCreate(&d.e0) == cudaSuccess && cudaEventCreate(&d.e1) == cudaSuccess;
   d.loaded = true;  // so that unload frees whatever was allocated
   if (!ok) {
@@ -305,14 +441,17 @@ extern "C" int32_t hl_dense_unload_model(void) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
-  for (float** p : {&d.attn_norm, &d.ffn_norm, &d.out_norm, &d.q_norm, &d.k_norm, &d.x, &d.qkv, &d.logits}) {
+  for (float** p : {&d.attn_norm, &d.ffn_norm, &d.out_norm, &d.q_norm, &d.k_norm, &d.x, &d.qkv, &d.logits, &d.cand_v}) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
-  for (int32_t** p : {&d.tokens_d, &d.ctx_len_d, &d.table_d, &d.next_d}) {
+  for (int32_t** p : {&d.tokens_d, &d.ctx_len_d, &d.table_d, &d.next_d, &d.cand_i}) {
     if (*p) cudaFree(*p);
     *p = nullptr;
   }
+  if (d.graph) cudaGraphExecDestroy(d.graph);
+  d.graph = nullptr;
+  d.graph_kv = nullptr;
   if (d.pinned) cudaFreeHost(d.pinned);
   d.pinned = nullptr;
   if (d.e0) cudaEventDestroy(d.e0);
@@ -342,6 +481,7 @@ extern "C" int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, fl
   D_PASS(check_cache(cache));
   if (!logits_h) return dfail(HL_ERR_ARG, "null logits");
   if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
+  if (d.use_graph) return decode_graph(token, cache, logits_h, nullptr, nullptr);
   D_PASS(forward(&token, 1, cache->cur_len, cache, true));
   D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
   D_PASS(finish());
@@ -353,10 +493,10 @@ extern "C" int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cach
   D_PASS(check_cache(cache));
   if (!next_token) return dfail(HL_ERR_ARG, "null next_token");
   if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
+  if (d.use_graph) return decode_graph(token, cache, nullptr, next_token, gpu_ms);
   if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, d.ctx->stream));
   D_PASS(forward(&token, 1, cache->cur_len, cache, true));
-  argmax_first<<<1, 256, 0, d.ctx->stream>>>(d.logits, d.hp.n_vocab, d.next_d);
-  d.ctx->launches += 1;
+  launch_argmax(d.ctx->stream);
   if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, d.ctx->stream));
   D_CUDA(cudaMemcpyAsync(&d.pinned[2], d.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, d.ctx->stream));
   D_PASS(finish());

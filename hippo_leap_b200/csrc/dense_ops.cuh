@@ -6,6 +6,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "hl_device.cuh"
+
 namespace hl {
 
 // x[t][:] = float(table[token[t]][:])
@@ -22,35 +24,20 @@ __global__ void embedding_f16_kernel(const __half* __restrict__ table, const int
 // out[t][:] = fp16( x[t][:] * (1 / sqrt(mean(x[t]^2) + eps)) * w[:] ); one block per token row
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                            int dim, float eps, __half* __restrict__ out) {
-  __shared__ float red[8];
-  __shared__ float inv_s;
   const float* xr = x + static_cast<int64_t>(blockIdx.x) * dim;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < dim; i += 256) ss += xr[i] * xr[i];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float tot = 0.f;
-    for (int i = 0; i < 8; ++i) tot += red[i];
-    inv_s = 1.0f / sqrtf(tot / static_cast<float>(dim) + eps);
-  }
-  __syncthreads();
-  const float inv = inv_s;
+  const float inv = block_rms_inv_256(xr, dim, eps);
   __half* orow = out + static_cast<int64_t>(blockIdx.x) * dim;
   for (int i = threadIdx.x; i < dim; i += 256) orow[i] = __float2half_rn(xr[i] * inv * w[i]);
 }
 
-// h[t][f] = fp16( silu(gate) * up ), gate = gu[t][f], up = gu[t][n_ffn + f]  (one merged gate|up GEMM output, fp16)
+// h[t][f] = fp16( silu(gate) * up ), gate = gu[t][2f], up = gu[t][2f + 1]: the fp16 output of ONE GEMM whose weight
+// rows interleave gate and up
 __global__ void silu_mul_kernel(const __half* __restrict__ gu, int n_ffn, int64_t total, __half* __restrict__ h) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t t = idx / n_ffn, f = idx % n_ffn;
-  const float g = __half2float(gu[t * 2 * n_ffn + f]);
-  const float u = __half2float(gu[t * 2 * n_ffn + n_ffn + f]);
-  const float sig = 1.0f / (1.0f + expf(-g));
-  h[idx] = __float2half_rn(g * sig * u);
+  const __half2 p = reinterpret_cast<const __half2*>(gu)[t * n_ffn + f];
+  h[idx] = silu_mul_f16(__low2half(p), __high2half(p));
 }
 
 }  // namespace hl

@@ -7,6 +7,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <string>
@@ -20,6 +21,7 @@
 #include "host_common.h"
 #include "kv_append.cuh"
 #include "linear_f16.cuh"
+#include "linear_gemv.cuh"
 
 using namespace hl;
 
@@ -673,6 +675,80 @@ static int32_t make_map_2d(hl_ctx* ctx, CUtensorMap* map, const void* ptr, uint6
   return HL_OK;
 }
 
+// Launch of the decode GEMV (M <= 4, K % 8 == 0, 16-byte aligned W rows).  g.a / x per mode as in GemvArgs.
+static int32_t launch_gemv_fused(hl_ctx* ctx, GemvArgs p) {
+  const LinearArgs& g = p.g;
+  constexpr int R = 4;
+  const int64_t groups = (g.N + R - 1) / R;
+  int ks = 1;
+  while (ks < 8 && groups * ks < static_cast<int64_t>(ctx->n_sm) * 12 && g.K / (ks * 2) >= 256) ks *= 2;
+  p.ks = ks;
+  p.kslice = ((g.K + ks - 1) / ks + 255) / 256 * 256;
+  const size_t smem = static_cast<size_t>(g.M) * g.K * 2 + 8 * 4 * R * sizeof(float);
+  if (smem > 200 * 1024) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode projection: M * K too large for shared memory");
+  const unsigned grid = static_cast<unsigned>((groups * ks + 7) / 8);
+  auto kern = g.M == 1 ? linear_gemv_fused_kernel<1, R> : (g.M == 2 ? linear_gemv_fused_kernel<2, R> : linear_gemv_fused_kernel<4, R>);
+  static bool configured[16][3] = {};
+  bool& conf = configured[ctx->device & 15][g.M == 1 ? 0 : (g.M == 2 ? 1 : 2)];
+  if (smem > 48 * 1024 && !conf) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    conf = true;
+  }
+  // programmatic stream serialisation: the kernel may start while its predecessor drains; it prefetches weights,
+  // then waits for the predecessor (griddepcontrol.wait) before it touches activations
+  static const bool no_pdl = getenv("HL_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  HL_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
+int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const void* a, int64_t lda, const float* norm_w,
+                               float eps, const void* w, int64_t ldw, void* out, int32_t out_dtype, int64_t ldo,
+                               const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!a || !w || !out || (mode == kGemvRmsNorm && !norm_w)) return hl_fail(ctx, HL_ERR_ARG, "decode projection: null pointer");
+  if (M <= 0 || M > 4 || N <= 0 || K <= 0 || (K & 7) || (ldw & 7) || ldw >= (1 << 28) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode projection: needs 1 <= M <= 4, K % 8 == 0 and 16-byte aligned weight rows");
+  if (mode < kGemvPlain || mode > kGemvRmsNorm) return hl_fail(ctx, HL_ERR_ARG, "decode projection: bad prologue mode");
+  if (swiglu && ((N & 1) || resid || out_dtype != HL_DTYPE_F16))
+    return hl_fail(ctx, HL_ERR_ARG, "decode projection: the SwiGLU epilogue needs an even N, fp16 output and no residual");
+  if (lda < K || ldw < K || ldo < (swiglu ? N / 2 : N) || (resid && ldr < N))
+    return hl_fail(ctx, HL_ERR_ARG, "decode projection: leading dimension too small");
+  HL_CUDA(ctx, cudaSetDevice(ctx->device));
+  GemvArgs p{};
+  p.g.a = mode == kGemvRmsNorm ? nullptr : static_cast<const __half*>(a);
+  p.x = mode == kGemvRmsNorm ? static_cast<const float*>(a) : nullptr;
+  p.ldx = lda;
+  p.norm_w = norm_w;
+  p.eps = eps;
+  p.mode = mode;
+  p.swiglu = swiglu;
+  p.g.w = static_cast<const __half*>(w);
+  p.g.out = out;
+  p.g.resid = resid;
+  p.g.lda = lda;
+  p.g.ldw = ldw;
+  p.g.ldo = ldo;
+  p.g.ldr = ldr;
+  p.g.M = M;
+  p.g.N = N;
+  p.g.K = K;
+  p.g.out_dtype = out_dtype;
+  p.g.status = ctx->status_d;
+  return launch_gemv_fused(ctx, p);
+}
+
 extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out,
                                       int32_t out_dtype, int64_t ldo, const float* resid, int64_t ldr, int32_t M,
                                       int32_t N, int32_t K, float* gpu_ms) {
@@ -698,6 +774,15 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
   g.status = ctx->status_d;
   int32_t rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
+  if (M <= 4 && !(K & 7) && !(ldw & 7) && ldw < (1 << 28) && !(reinterpret_cast<uintptr_t>(w) & 15) &&
+      static_cast<size_t>(M) * K * 2 + 512 <= 200 * 1024) {
+    GemvArgs p{};
+    p.g = g;
+    p.mode = kGemvPlain;
+    rc = launch_gemv_fused(ctx, p);
+    if (rc != HL_OK) return rc;
+    return hl_end_timing(ctx, gpu_ms);
+  }
   if (M < 16) {
     const unsigned grid = static_cast<unsigned>((static_cast<int64_t>(N) * 32 + 255) / 256);
     if (M <= 4)

@@ -150,6 +150,34 @@ __device__ __forceinline__ float apply_gate(const View& gate, int64_t t, int64_t
   return (1.0f / (1.0f + expf(-g))) * x;
 }
 
+// 1 / sqrt(mean(x^2) + eps) of one fp32 row, computed by a whole 256-thread block (every thread gets the value).
+// One fixed order of additions: thread-strided partial sums, warp butterfly, eight warp sums added by index.
+__device__ __forceinline__ float block_rms_inv_256(const float* __restrict__ xr, int dim, float eps) {
+  __shared__ float red[8];
+  __shared__ float inv_s;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += 256) ss += xr[i] * xr[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __syncthreads();  // a previous call's readers are done with red / inv_s
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    inv_s = 1.0f / sqrtf(tot / static_cast<float>(dim) + eps);
+  }
+  __syncthreads();
+  return inv_s;
+}
+
+// fp16( silu(gate) * up ), silu(g) = g / (1 + expf(-g))   (siluMulKernel, naive.nim:2179-2197)
+__device__ __forceinline__ __half silu_mul_f16(__half gate, __half up) {
+  const float g = __half2float(gate), u = __half2float(up);
+  const float sig = 1.0f / (1.0f + expf(-g));
+  return __float2half_rn(g * sig * u);
+}
+
 // ---- row prologue: (RMSNorm) -> RoPE -------------------------------------------------------
 // One WARP transforms one head row x[0..HD) held in shared memory as float32, in place.
 //   norm : x <- x * (1/sqrt(mean(x^2) + eps)) * w        (naive.nim:2906-2917; tensor.nim:92-100)

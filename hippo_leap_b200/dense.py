@@ -36,6 +36,7 @@ DENSE_SYMBOLS = {
     "hl_dense_forward_prefill": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode": (_i32, [_i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode_token_timed": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32), _f32p]),
+    "hl_dense_set_decode_graph": (_i32, [_i32]),
     "hl_dense_last_error": (C.c_char_p, []),
 }
 _typed = False
@@ -144,6 +145,10 @@ def forwardDecodeTokenTimed(m: DenseModel, token: int, cache: KvCache):
     nxt, ms = _i32(), C.c_float()
     _check(_lib().hl_dense_forward_decode_token_timed(int(token), C.byref(cache.c), C.byref(nxt), C.byref(ms)))
     return nxt.value, ms.value
+
+
+def setDecodeGraph(enabled: bool):
+    _check(_lib().hl_dense_set_decode_graph(int(enabled)))
 
 
 def forwardDecodeToken(m: DenseModel, token: int, cache: KvCache) -> int:

@@ -121,6 +121,10 @@ int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache
 int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
 /* forwardDecodeTokenTimed: argmax on the device, optional device time of the step. */
 int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token, float* gpu_ms);
+/* Decode steps replay one captured CUDA graph per token (default on); 0 queues the kernels one by one instead.
+ * Same results either way.  The reference's megakernel backend replays a HIP graph per token the same way
+ * (src/hippo_leap/backends/megakernel.nim:2458-2479). */
+int32_t hl_dense_set_decode_graph(int32_t enabled);
 const char* hl_dense_last_error(void);
 
 #ifdef __cplusplus

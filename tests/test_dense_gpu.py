@@ -64,9 +64,10 @@ CASES = {
 
 
 @pytest.mark.parametrize("name", list(CASES))
-@pytest.mark.parametrize("prompt_len", [5, 150])
-def test_dense_model_against_oracle(name, prompt_len):
+@pytest.mark.parametrize("prompt_len,graph", [(5, True), (150, True), (3, False)])
+def test_dense_model_against_oracle(name, prompt_len, graph):
     hp, qk_norm = CASES[name]
+    D.setDecodeGraph(graph)
     steps, seed = 6, 11
     m = D.random_dense_model(hp, seed, qk_norm)
     max_len = prompt_len + steps + 2
@@ -106,6 +107,30 @@ def test_dense_model_against_oracle(name, prompt_len):
             assert cache.curLen == prompt_len + step + 1
         assert cache.curLen <= max_len
     finally:
+        D.unloadModelBackend()
+
+
+def test_dense_graph_replay_equals_plain_launches():
+    """The captured decode step and the same kernels queued one by one give bit-identical logits."""
+    hp, qk_norm = CASES["qwen3_hd128_qknorm"]
+    m = D.random_dense_model(hp, 4, qk_norm)
+    cache = D.initKvCache(hp, 64)
+    D.loadModelBackend(m, hp)
+    try:
+        prompt = np.arange(1, 31, dtype=np.int32)
+        runs = []
+        for graph in (True, False):
+            D.setDecodeGraph(graph)
+            cache.curLen = 0
+            out = [D.forwardPrefill(m, prompt, cache)]
+            tok = D.argmaxLast(out[0], hp.nVocab)
+            for _ in range(5):
+                out.append(D.forwardDecode(m, tok, cache))
+                tok = D.argmaxLast(out[-1], hp.nVocab)
+            runs.append(np.concatenate(out))
+        assert np.array_equal(runs[0], runs[1])
+    finally:
+        D.setDecodeGraph(True)
         D.unloadModelBackend()
 
 
