@@ -43,6 +43,7 @@ BACKEND_SYMBOLS = {
     "hl_backend_load_model": (_i32, [_i32, C.POINTER(HParamsC), C.POINTER(WeightsC)]),
     "hl_backend_unload_model": (_i32, []),
     "hl_backend_forward_prefill": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
+    "hl_backend_forward_prefill_chunk": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
     "hl_backend_forward_decode": (_i32, [_i32, C.POINTER(KvCacheC), _f32p]),
     "hl_backend_forward_decode_token": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32)]),
     "hl_backend_forward_decode_token_timed": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32), _f32p]),
@@ -160,6 +161,16 @@ def forwardPrefill(m: Model, tokens, cache: KvCache) -> np.ndarray:
     logits = np.empty((1, m.hparams.nVocab), np.float32)
     _check(_lib().hl_backend_forward_prefill(toks.ctypes.data_as(C.POINTER(_i32)), toks.size, C.byref(cache.c),
                                              logits.ctypes.data_as(_f32p)))
+    return logits
+
+
+def forwardPrefillChunk(m: Model, tokens, cache: KvCache) -> np.ndarray:
+    """Prefill continuing at position cache.curLen (chunked prompt, or a shared prefix kept in the cache); logits of the
+    last token.  The reference has no such proc: its forwardPrefill restarts at position 0."""
+    toks = np.ascontiguousarray(tokens, np.int32)
+    logits = np.empty((1, m.hparams.nVocab), np.float32)
+    _check(_lib().hl_backend_forward_prefill_chunk(toks.ctypes.data_as(C.POINTER(_i32)), toks.size, C.byref(cache.c),
+                                                   logits.ctypes.data_as(_f32p)))
     return logits
 
 

@@ -477,6 +477,19 @@ extern "C" int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, 
   return HL_OK;
 }
 
+extern "C" int32_t hl_dense_forward_prefill_chunk(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h) {
+  D_PASS(check_cache(cache));
+  if (!tokens_h || !logits_h) return dfail(HL_ERR_ARG, "null argument");
+  if (n <= 0) return dfail(HL_ERR_ARG, "prefill requires at least one token");
+  if (cache->cur_len < 0) return dfail(HL_ERR_ARG, "negative cur_len");
+  if (static_cast<int64_t>(cache->cur_len) + n > cache->max_len) return dfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
+  D_PASS(forward(tokens_h, n, cache->cur_len, cache, false));
+  D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_PASS(finish());
+  cache->cur_len += n;
+  return HL_OK;
+}
+
 extern "C" int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h) {
   D_PASS(check_cache(cache));
   if (!logits_h) return dfail(HL_ERR_ARG, "null logits");

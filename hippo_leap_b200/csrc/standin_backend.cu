@@ -373,6 +373,19 @@ extern "C" int32_t hl_backend_forward_prefill(const int32_t* tokens_h, int32_t n
   return HL_OK;
 }
 
+extern "C" int32_t hl_backend_forward_prefill_chunk(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h) {
+  B_PASS(check_cache(cache));
+  if (!tokens_h || !logits_h) return bfail(HL_ERR_ARG, "null argument");
+  if (n <= 0) return bfail(HL_ERR_ARG, "prefill requires at least one token");
+  if (cache->cur_len < 0) return bfail(HL_ERR_ARG, "negative cur_len");
+  if (static_cast<int64_t>(cache->cur_len) + n > cache->max_len) return bfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
+  B_PASS(forward(tokens_h, n, cache->cur_len, cache, false));
+  B_CUDA(cudaMemcpyAsync(logits_h, g.logits_d, g.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, g.ctx->stream));
+  B_PASS(finish_status());
+  cache->cur_len += n;
+  return HL_OK;
+}
+
 static int32_t decode_common(int32_t token, hl_kv_cache* cache) {
   B_PASS(check_cache(cache));
   if (cache->cur_len >= cache->max_len) return bfail(HL_ERR_CAPACITY, "KV cache full");

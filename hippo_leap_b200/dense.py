@@ -34,6 +34,7 @@ DENSE_SYMBOLS = {
     "hl_dense_load_model": (_i32, [_i32, C.POINTER(DenseHParamsC), C.POINTER(DenseWeightsC)]),
     "hl_dense_unload_model": (_i32, []),
     "hl_dense_forward_prefill": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
+    "hl_dense_forward_prefill_chunk": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode": (_i32, [_i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode_token_timed": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32), _f32p]),
     "hl_dense_set_decode_graph": (_i32, [_i32]),
@@ -132,6 +133,15 @@ def forwardPrefill(m: DenseModel, tokens, cache: KvCache) -> np.ndarray:
     logits = np.empty((1, m.hparams.nVocab), np.float32)
     _check(_lib().hl_dense_forward_prefill(toks.ctypes.data_as(C.POINTER(_i32)), toks.size, C.byref(cache.c),
                                            logits.ctypes.data_as(_f32p)))
+    return logits
+
+
+def forwardPrefillChunk(m: DenseModel, tokens, cache: KvCache) -> np.ndarray:
+    """Prefill continuing at position cache.curLen (chunked prompt, or a shared prefix kept in the cache)."""
+    toks = np.ascontiguousarray(tokens, np.int32)
+    logits = np.empty((1, m.hparams.nVocab), np.float32)
+    _check(_lib().hl_dense_forward_prefill_chunk(toks.ctypes.data_as(C.POINTER(_i32)), toks.size, C.byref(cache.c),
+                                                 logits.ctypes.data_as(_f32p)))
     return logits
 
 

@@ -65,6 +65,12 @@ int32_t hl_backend_unload_model(void);
  * (naive.nim:4075-4076, 4586-4587).  Errors as naive.nim:3969-3976: empty prompt, prompt longer
  * than the cache. */
 int32_t hl_backend_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
+/* Chunked prefill / prefix reuse -- no counterpart in the reference, whose forwardPrefill always restarts at
+ * position 0 (naive.nim:3125; the wish is in docs/v2.5.md:40-47).  The n tokens take positions cache.cur_len ..
+ * cache.cur_len + n - 1 on top of whatever the cache already holds up to cur_len; cur_len += n; logits of the last
+ * of them.  A long prompt can be fed in pieces, and a caller that resets cur_len to the length of a shared prefix
+ * re-uses that prefix's keys and values. */
+int32_t hl_backend_forward_prefill_chunk(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
 /* forwardDecode(m, token, cache): naive.nim:4592-5100.  pos = cache.cur_len; "KV cache full"
  * when pos >= max_len (naive.nim:4598-4599). */
 int32_t hl_backend_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
@@ -117,6 +123,8 @@ int32_t hl_dense_load_model(int32_t device, const hl_dense_hparams* hp, const hl
 int32_t hl_dense_unload_model(void);
 /* forwardPrefill: logits of the last position [n_vocab]; starts at position 0, sets cur_len = n. */
 int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
+/* Chunked prefill / prefix reuse on the dense model: as hl_backend_forward_prefill_chunk. */
+int32_t hl_dense_forward_prefill_chunk(const int32_t* tokens_h, int32_t n, hl_kv_cache* cache, float* logits_h);
 /* forwardDecode: one token at position cache.cur_len; "KV cache full" at capacity. */
 int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
 /* forwardDecodeTokenTimed: argmax on the device, optional device time of the step. */

@@ -190,3 +190,40 @@ def test_decode_graph_replay_equals_plain_launches():
         B.setDecodeGraph(True)
         B.freeKvCache(cache)
         B.unloadModelBackend()
+
+
+def test_chunked_prefill_and_prefix_reuse_stand_in_model():
+    """forwardPrefillChunk: a prompt fed in pieces whose positions continue at curLen (RoPE at pos + p, a causal mask
+    that is not square), and a new tail on a kept prefix; the oracle is driven the same way."""
+    hp = B.HParams(nVocab=512, nLayer=2, nHead=16, nHeadKv=4, headDim=128, ropeFreqBase=1e6)
+    m = B.standin_model(hp, 9, True)
+    g = np.random.Generator(np.random.PCG64([9, 1]))
+    prefix, tail_a, tail_b = (g.integers(0, hp.nVocab, n).astype(np.int32) for n in (200, 130, 33))
+    max_len = 340
+    cache = B.initKvCache(hp, max_len)
+    B.loadModelBackend(m, hp)
+    try:
+        ref = OracleModel(m, max_len, hp.ropeMode)
+        cache.curLen = 0
+        B.forwardPrefillChunk(m, prefix, cache)
+        B.forwardPrefillChunk(m, tail_a[:1], cache)  # a one-token piece goes through the prefill kernels too
+        got = B.forwardPrefillChunk(m, tail_a[1:], cache)
+        assert cache.curLen == 330
+        ref.forward(prefix)
+        ref.forward(tail_a[:1])
+        want = ref.forward(tail_a[1:])
+        assert_parity(got, want, "chunked prefill", max_abs_tol=2e-3 * float(np.abs(want).max()), rel_l2_tol=1e-3)
+        cache.curLen = 0
+        one_shot = B.forwardPrefill(m, np.concatenate([prefix, tail_a]), cache)
+        assert_parity(got, one_shot, "chunked vs one-shot", max_abs_tol=2e-3 * float(np.abs(want).max()), rel_l2_tol=1e-3)
+        cache.curLen = 200
+        for c in ref.caches:
+            c.cur_len = 200
+        got_b, want_b = B.forwardPrefillChunk(m, tail_b, cache), ref.forward(tail_b)
+        assert cache.curLen == 233
+        assert_parity(got_b, want_b, "prefix reuse", max_abs_tol=2e-3 * float(np.abs(want_b).max()), rel_l2_tol=1e-3)
+        with pytest.raises(ValueError, match="exceeds KV cache capacity"):
+            B.forwardPrefillChunk(m, np.zeros(200, np.int32), cache)
+    finally:
+        B.freeKvCache(cache)
+        B.unloadModelBackend()

@@ -134,6 +134,50 @@ def test_dense_graph_replay_equals_plain_launches():
         D.unloadModelBackend()
 
 
+@pytest.mark.parametrize("name", ["llama_hd64", "qwen3_hd128_qknorm"])
+def test_dense_chunked_prefill_and_prefix_reuse(name):
+    """A prompt fed in pieces (positions continue at curLen) and a second prompt on a kept prefix, against the oracle
+    fed the same way, and against the one-shot prefill."""
+    hp, qk_norm = CASES[name]
+    m = D.random_dense_model(hp, 21, qk_norm)
+    g = np.random.Generator(np.random.PCG64([21, 1]))
+    prefix, tail_a, tail_b = (g.integers(0, hp.nVocab, n).astype(np.int32) for n in (150, 77, 40))
+    max_len = 150 + 77 + 8
+    cache = D.initKvCache(hp, max_len)
+    D.loadModelBackend(m, hp)
+    try:
+        one_shot = D.forwardPrefill(m, np.concatenate([prefix, tail_a]), cache)
+        # chunked: 150 + 64 + 13, unequal pieces, the second and third start inside a 128-token page
+        cache.curLen = 0
+        D.forwardPrefillChunk(m, prefix, cache)
+        D.forwardPrefillChunk(m, tail_a[:64], cache)
+        chunked = D.forwardPrefillChunk(m, tail_a[64:], cache)
+        assert cache.curLen == 227
+        ref = OracleDense(m, max_len, True)
+        ref.forward(prefix)
+        ref.forward(tail_a[:64])
+        want = ref.forward(tail_a[64:])
+        scale = float(np.abs(want).max())
+        assert_parity(chunked, want, "chunked prefill vs oracle", max_abs_tol=3e-3 * scale, rel_l2_tol=1.5e-3)
+        assert_parity(chunked, one_shot, "chunked vs one-shot prefill", max_abs_tol=2e-3 * scale, rel_l2_tol=1e-3)
+        # prefix reuse: keep the first 150 positions, replace what follows
+        cache.curLen = 150
+        reused = D.forwardPrefillChunk(m, tail_b, cache)
+        assert cache.curLen == 190
+        for c in ref.caches:
+            c.cur_len = 150
+        want_b = ref.forward(tail_b)
+        assert_parity(reused, want_b, "prefix reuse vs oracle", max_abs_tol=3e-3 * float(np.abs(want_b).max()),
+                      rel_l2_tol=1.5e-3)
+        tok = D.argmaxLast(reused, hp.nVocab)
+        nxt = D.forwardDecode(m, tok, cache)
+        assert_parity(nxt, ref.forward([tok]), "decode after prefix reuse", max_abs_tol=3e-3 * scale, rel_l2_tol=1.5e-3)
+        with pytest.raises(ValueError, match="exceeds KV cache capacity"):
+            D.forwardPrefillChunk(m, np.zeros(max_len, np.int32), cache)
+    finally:
+        D.unloadModelBackend()
+
+
 def test_dense_contract_errors():
     hp, _ = CASES["llama_hd64"]
     m = D.random_dense_model(hp, 3)
