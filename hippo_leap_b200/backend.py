@@ -224,11 +224,14 @@ class GenerateResult:
     gpuMs: float
 
 
-def generate(m: Model, cache: KvCache, promptTokens, maxTokens: int, maxContextLen: int | None = None,
-             stopTokenIds=()) -> GenerateResult:
+def generate(m, cache: KvCache, promptTokens, maxTokens: int, maxContextLen: int | None = None,
+             stopTokenIds=(), procs=None) -> GenerateResult:
     """The reference's generate loop (src/hippo_leap/inference.nim:51-97) on token ids: reset curLen,
-    one prefill, argmax, then forwardDecodeTokenTimed until maxTokens or a stop token."""
+    one prefill, argmax, then forwardDecodeTokenTimed until maxTokens or a stop token.  ``procs`` is the module whose
+    forwardPrefill / forwardDecodeTokenTimed are driven (this one by default, ``dense`` for the dense model)."""
     import time
+    forwardPrefill = globals()["forwardPrefill"] if procs is None else procs.forwardPrefill
+    forwardDecodeTokenTimed = globals()["forwardDecodeTokenTimed"] if procs is None else procs.forwardDecodeTokenTimed
     t0 = time.perf_counter()
     cache.curLen = 0
     prompt = list(promptTokens)

@@ -178,6 +178,29 @@ def test_dense_chunked_prefill_and_prefix_reuse(name):
         D.unloadModelBackend()
 
 
+def test_dense_generate_loop_and_bench_cli(capsys):
+    """The reference's generate loop and bench table (inference.nim:51-97, cmd_bench.nim:93-136) on the dense model."""
+    from hippo_leap_b200 import backend as B
+    from hippo_leap_b200 import cmd_bench
+    hp, _ = CASES["llama_hd64"]
+    m = D.random_dense_model(hp, 2)
+    cache = D.initKvCache(hp, 64)
+    D.loadModelBackend(m, hp)
+    try:
+        res = B.generate(m, cache, [1, 2, 3, 4, 5], 8, procs=D)
+        assert res.completionTokens == 8 and res.gpuMs > 0 and cache.curLen == 5 + 7
+        assert B.generate(m, cache, [1, 2, 3, 4, 5], 8, procs=D).tokens == res.tokens
+    finally:
+        D.freeKvCache(cache)
+        D.unloadModelBackend()
+    assert cmd_bench.main(["--model", "dense", "--config", "1", "--layers", "2", "--emb", "256", "--ffn", "512", "--vocab",
+                           "1000", "--prompt-tokens", "20", "--tokens", "6", "--runs", "2", "--warmup", "1", "--context",
+                           "64"]) == 0
+    out = capsys.readouterr().out
+    assert "dense layer stack" in out and " Run  Tokens  Time(ms)   tok/s   GPU(ms)  gpu tok/s" in out
+    assert "Wall:" in out and "GPU :" in out
+
+
 def test_dense_contract_errors():
     hp, _ = CASES["llama_hd64"]
     m = D.random_dense_model(hp, 3)
