@@ -59,6 +59,9 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, DecodeArgs a) {
   using Cfg = DecodeCfg<HD, NW, STAGES>;
+  // a kernel queued behind this one with programmatic stream serialisation (an output projection that first
+  // prefetches its weights) may start now; it still waits for this whole grid before it reads the attention output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int ctx = a.ctx_lens[b];
   const int t_begin = chunk * a.chunk_tokens;

@@ -458,11 +458,12 @@ static int32_t launch_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const Decode
 
 int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_kv, int32_t max_ctx) {
   if (ctx->decode_chunk > 0) return ctx->decode_chunk;
-  // Aim at about eight CTAs per SM over the whole grid; never below one 64-token stage.
+  // Aim at about eight CTAs per SM over the whole grid; never below two 64-token stages (a single short sequence
+  // is latency-bound: fewer partials to merge beat more CTAs).
   const int64_t base = static_cast<int64_t>(batch) * n_head_kv;
   int64_t chunk = (static_cast<int64_t>(max_ctx) * base) / (8 * ctx->n_sm);
   chunk = ((chunk + 63) / 64) * 64;
-  if (chunk < 64) chunk = 64;
+  if (chunk < 128) chunk = 128;
   if (chunk > 1024) chunk = 1024;
   return static_cast<int32_t>(chunk);
 }

@@ -50,6 +50,10 @@ def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm, k
     hl_ctx.kv_append_seq(kv, 0, shape, tk, tv, 0, tt)
     out = hl_ctx.attn_prefill(kv, 0, shape, tq, 0, tt)
     got = out.cpu().numpy()
+    # host-buffer form (append + prefill, host in / host out) equals the device form
+    out_h = torch.full((S, n_head, hd), float("nan"))
+    hl_ctx.prefill_host(kv, 0, shape, torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v), 0, tt, out_h)
+    assert np.array_equal(out_h.numpy(), got), "prefill_host differs from the device form"
     hl_ctx.set_tuning(0, 0)
     want = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw)
     want16 = oracle_seq(q, k, v, theta=theta, rope_mode=rope_mode, q_norm_w=qw, k_norm_w=kw, kv_fp16=True)
@@ -103,4 +107,15 @@ def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs,
     hl_ctx.set_tuning(0, 0)
     assert_parity(got, want, "decode vs fp32 oracle")
     assert_parity(got, want16, "decode vs fp16-KV oracle", 1e-3, 6e-4)
+    # the host-buffer form of the same step (append + decode, host in / host out): pageable buffers go through
+    # staged copies, page-locked ones are read and written by the kernels in place; both equal the device form
+    hl_ctx.set_tuning(chunk, 0)
+    for pin in (False, True):
+        bufs = [torch.from_numpy(x.copy()) for x in (qn, kn, vn)]
+        out_h = torch.full((B, n_head, hd), float("nan"))
+        if pin:
+            bufs, out_h = [b.pin_memory() for b in bufs], out_h.pin_memory()
+        hl_ctx.decode_step_host(kv, 0, shape, *bufs, tctx, int(ctxs.max()), ttab, out_h)
+        assert np.array_equal(out_h.numpy(), got), f"host form (pinned={pin}) differs from the device form"
+    hl_ctx.set_tuning(0, 0)
     kv.destroy()
