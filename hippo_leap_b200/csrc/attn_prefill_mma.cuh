@@ -51,8 +51,8 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, PrefillArgs a) {
   using Cfg = PrefillMmaCfg<HD, NW, STAGES>;
-  const int q_tile_idx = gridDim.x - 1 - blockIdx.x;  // longest first
-  const int h = blockIdx.y;
+  const int q_tile_idx = gridDim.y - 1 - blockIdx.y;  // heads fastest, query tiles longest first over the whole grid
+  const int h = blockIdx.x;
   const int kvh = h / a.group;
   const int t0 = q_tile_idx * Cfg::kBM;
   const int rows_live = min(Cfg::kBM, a.n_tok - t0);

@@ -240,8 +240,12 @@ __global__ void __launch_bounds__(384, 1)
   constexpr int SK = Cfg::kStagesK, SV = Cfg::kStagesV;
   const PrefillArgs& a = ta.p;
   const bool fast_prologue = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
-  const int q_blk = gridDim.x - 1 - blockIdx.x;  // longest first
-  const int h = blockIdx.y;
+  // Heads vary fastest and query blocks run from the last (most keys) to the first, so the launch order is
+  // longest-first over the WHOLE grid: the short blocks of every head fill the tail.  (With query blocks fastest the
+  // last head's long blocks start last and run with most SMs idle: 0.71 ms instead of 0.51 ms at 8192 tokens.)
+  // Neighbouring CTAs are the query heads of one KV head, so they share K/V tiles in L2.
+  const int q_blk = gridDim.y - 1 - blockIdx.y;
+  const int h = blockIdx.x;
   const int kvh = h / a.group;
   const int t0 = q_blk * 256;
 
@@ -754,7 +758,7 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
   if (rc != HL_OK) return rc;
   const bool wide = kv->block_tokens % 128 == 0;
   ta.box_rows = wide ? 128 : 16;
-  dim3 grid((a.n_tok + 255) / 256, a.n_head);
+  dim3 grid(a.n_head, (a.n_tok + 255) / 256);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(wide ? kv->k_map128[layer] : kv->k_map[layer],
                                                               wide ? kv->v_map128[layer] : kv->v_map[layer], ta);
   ctx->launches++;

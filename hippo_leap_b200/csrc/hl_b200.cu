@@ -562,7 +562,7 @@ static int32_t launch_prefill_mma(hl_ctx* ctx, hl_kv* kv, int32_t layer, const P
     HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured[ctx->device & 15] = true;
   }
-  dim3 grid((a.n_tok + Cfg::kBM - 1) / Cfg::kBM, a.n_head);
+  dim3 grid(a.n_head, (a.n_tok + Cfg::kBM - 1) / Cfg::kBM);
   kern<<<grid, (NW + 1) * 32, Cfg::kSmemBytes, ctx->stream>>>(kv->k_map[layer], kv->v_map[layer], a);
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
@@ -585,6 +585,7 @@ static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
     return hl_fail(ctx, HL_ERR_CAPACITY, "prefill exceeds KV cache capacity (%d + %d > %lld)", start_pos, n_tok,
                    static_cast<long long>(n_blocks_in_table) * kv->block_tokens);
   if (s->n_head > 65535) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: too many heads");
+  if (n_tok > 65535 * 128) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: more than 65535 query tiles in one call");
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
 
   PrefillArgs a{};
