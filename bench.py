@@ -245,22 +245,60 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
 
 
 def extra_linear(ctx, torch, device, peaks):
-    """The dense fp16 projection next to the hot path: Wo-shaped GEMM at config 3 size and its decode GEMV."""
+    """The dense fp16 projection next to the hot path: a Wo-shaped GEMM at config 3 size, and the decode projections
+    of Llama-3.2-1B (M = 1) timed as chains of 16 launches over 16 different weight matrices (more than L2 holds)
+    replayed from one CUDA graph, so that the figures are device time, not the launch rate of this script."""
+    import hippo_leap_b200 as hl
     gen = torch.Generator(device=device)
     gen.manual_seed(7)
     res = {}
-    for name, (M, N, K) in {"gemm_8192x4096x4096": (8192, 4096, 4096), "gemv_1x4096x4096": (1, 4096, 4096)}.items():
-        a = torch.randn((M, K), generator=gen, device=device).half()
-        w = (torch.randn((N, K), generator=gen, device=device) / K ** 0.5).half()
-        out = torch.empty((M, N), dtype=torch.float32, device=device)
-        for _ in range(3):
-            ctx.linear_f16(a, w, out)
-        n = 20
-        ms = timed_loop(torch, lambda: ctx.linear_f16(a, w, out), n) / n
-        fl = 2.0 * M * N * K
-        by = (M * K + N * K) * 2 + M * N * 4
-        res[name] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"],
-                     "gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    M, N, K = 8192, 4096, 4096
+    a = torch.randn((M, K), generator=gen, device=device).half()
+    w = (torch.randn((N, K), generator=gen, device=device) / K ** 0.5).half()
+    out = torch.empty((M, N), dtype=torch.float32, device=device)
+    for _ in range(3):
+        ctx.linear_f16(a, w, out)
+    n = 20
+    ms = timed_loop(torch, lambda: ctx.linear_f16(a, w, out), n) / n
+    fl = 2.0 * M * N * K
+    res[f"gemm_{M}x{N}x{K}"] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12,
+                                "frac_of_tensor_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+    del a, w, out
+    side = torch.cuda.Stream(device=device)
+    ctx2 = hl.Context(device.index or 0, side)
+    try:
+        for name, (N, K, L) in {"qkv_3072x2048": (3072, 2048, 16), "wo_2048x2048": (2048, 2048, 16),
+                                "gate_up_16384x2048": (16384, 2048, 16), "down_2048x8192": (2048, 8192, 16),
+                                "vocab_128256x2048": (128256, 2048, 2)}.items():
+            ws = (torch.randn((L, N, K), generator=gen, device=device) / K ** 0.5).half()
+            a = torch.randn((1, K), generator=gen, device=device).half()
+            out = torch.empty((1, N), dtype=torch.float32, device=device)
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                for l in range(L):
+                    ctx2.linear_f16(a, ws[l], out)
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for l in range(L):
+                        ctx2.linear_f16(a, ws[l], out)
+                for _ in range(3):
+                    g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 20
+                e0.record(side)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(side)
+                side.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+            by = N * K * 2
+            res["gemv_" + name] = {"us_per_launch": us, "weight_gbs": by / (us * 1e-6) / 1e9,
+                                   "frac_of_hbm_peak": by / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+            del ws, a, out, g
+            torch.cuda.empty_cache()
+    finally:
+        ctx2.close()
     return res
 
 
