@@ -164,8 +164,21 @@ __device__ __forceinline__ void load_vec(const View& v, int64_t t, int64_t h, in
     }
   } else {
     const __half* p = static_cast<const __half*>(v.ptr) + off;
+    if ((reinterpret_cast<uintptr_t>(p) & (VEC * 2 - 1)) == 0) {
+      if constexpr (VEC == 4) {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+        x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+      } else {
+        const uint32_t q = *reinterpret_cast<const uint32_t*>(p);
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q));
+        x[0] = lo.x; x[1] = lo.y;
+      }
+    } else {
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) x[e] = __half2float(p[e]);
+      for (int e = 0; e < VEC; ++e) x[e] = __half2float(p[e]);
+    }
   }
 }
 
@@ -433,54 +446,92 @@ __global__ void __launch_bounds__(384, 1)
       const bool fast = fast_prologue;
       float* xrow = reinterpret_cast<float*>(gen + Cfg::kRowOff) + warp * HD;
       if (fast) {
-        // R rows per pass with all their global loads issued before any arithmetic: a warp that walked
-        // its 32 rows one dependent load at a time would spend most of the prologue waiting on HBM.
-        constexpr int R = 8;
+        // All 32 rows of the warp are requested before any arithmetic (one trip to HBM, not one per batch of rows),
+        // and the cos / sin pairs are not loaded per row -- that would double the bytes -- but taken exactly from the
+        // table every eighth row and advanced by one position per row with a complex multiply by (cos t, sin t) of
+        // position 1: at most seven steps, ~1e-6 absolute drift, far inside the fp16 rounding of Q.
+        constexpr int NA = VEC;  // angle slots per lane (interleaved pairing uses VEC / 2 of them)
         const int d0 = lane * VEC;
         const int last_pos = a.start_pos + a.n_tok - 1;
-        for (int rb = 0; rb < 32; rb += R) {
-          float x[R][VEC];
-          float2 cs[R][VEC];  // interleaved uses VEC/2 of them, split-half VEC
+        const int row0 = (warp & 3) * 32;
+        const int tt0 = t0 + 128 * t + row0;
+        const bool inter = a.rope_mode == HL_ROPE_INTERLEAVED;
+        float x[32][VEC];
 #pragma unroll
-          for (int u = 0; u < R; ++u) {
-            const int tt = t0 + 128 * t + (warp & 3) * 32 + rb + u;
-            if (tt < a.n_tok) {
-              load_vec<VEC>(a.q, tt, h, d0, x[u]);
-            } else {
+        for (int u = 0; u < 32; ++u) {
+          if (tt0 + u < a.n_tok) {
+            load_vec<VEC>(a.q, tt0 + u, h, d0, x[u]);
+          } else {
 #pragma unroll
-              for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
-            }
-            const float2* csr = ta.cs_table + static_cast<int64_t>(min(a.start_pos + tt, last_pos)) * (HD / 2);
-            if (a.rope_mode == HL_ROPE_INTERLEAVED) {
-#pragma unroll
-              for (int e = 0; e < VEC; e += 2) cs[u][e >> 1] = csr[(d0 + e) >> 1];
-            } else {
-#pragma unroll
-              for (int e = 0; e < VEC; ++e) cs[u][e] = csr[(d0 + e) & (HD / 2 - 1)];
-            }
+            for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
           }
+        }
+        int ai[NA];
+#pragma unroll
+        for (int e = 0; e < NA; ++e) ai[e] = inter ? ((d0 >> 1) + (e < VEC / 2 ? e : 0)) : ((d0 + e) & (HD / 2 - 1));
+        float2 step[NA], cs8[4][NA];
+#pragma unroll
+        for (int e = 0; e < NA; ++e) step[e] = ta.cs_table[(HD / 2) + ai[e]];  // position 1
+#pragma unroll
+        for (int b8 = 0; b8 < 4; ++b8) {
+          const float2* csr = ta.cs_table + static_cast<int64_t>(min(a.start_pos + tt0 + 8 * b8, last_pos)) * (HD / 2);
+#pragma unroll
+          for (int e = 0; e < NA; ++e) cs8[b8][e] = csr[ai[e]];
+        }
+        float w[VEC];
+        if (a.q_norm_w != nullptr) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) w[e] = a.q_norm_w[d0 + e];
+        }
+        // Two warps share a scheduler here, so latency is hidden by independent instructions of ONE warp: the rows
+        // are worked on eight at a time (while the later rows are still on their way from memory), and every step
+        // runs over the eight rows before the next dependent step starts.  1/sqrt is the hardware approximation
+        // (2 ulp): the exact sqrtf + divide pair is a call with branches that serialises the rows (4 us per CTA),
+        // and the result is rounded to fp16 a few lines further down.
+#pragma unroll
+        for (int b8 = 0; b8 < 4; ++b8) {
           if (a.q_norm_w != nullptr) {
-            float w[VEC];
+            float ss[8];
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) w[e] = a.q_norm_w[d0 + e];
+            for (int k = 0; k < 8; ++k) {
+              ss[k] = 0.f;
 #pragma unroll
-            for (int u = 0; u < R; ++u) {
-              float ss = 0.f;
+              for (int e = 0; e < VEC; ++e) ss[k] += x[8 * b8 + k][e] * x[8 * b8 + k][e];
+            }
 #pragma unroll
-              for (int e = 0; e < VEC; ++e) ss += x[u][e] * x[u][e];
+            for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-              for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-              const float inv = 1.0f / sqrtf(ss / static_cast<float>(HD) + a.eps);
+              for (int k = 0; k < 8; ++k) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], o);
+            }
 #pragma unroll
-              for (int e = 0; e < VEC; ++e) x[u][e] = x[u][e] * inv * w[e];
+            for (int k = 0; k < 8; ++k) {
+              const float inv = rsqrtf(ss[k] * (1.0f / static_cast<float>(HD)) + a.eps);
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) x[8 * b8 + k][e] = x[8 * b8 + k][e] * inv * w[e];
             }
           }
+          float other[8][VEC];
+          if (!inter) {
 #pragma unroll
-          for (int u = 0; u < R; ++u) {
-            if (a.rope_mode == HL_ROPE_INTERLEAVED) {
+            for (int k = 0; k < 8; ++k)
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) other[k][e] = __shfl_xor_sync(0xffffffffu, x[8 * b8 + k][e], 16);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int u = 8 * b8 + k;
+            float2* cs = cs8[b8];  // row 0 of the group: exact table values; then one complex multiply per row
+            if (k != 0) {
+#pragma unroll
+              for (int e = 0; e < NA; ++e) {
+                const float2 c0 = cs[e];
+                cs[e] = make_float2(c0.x * step[e].x - c0.y * step[e].y, c0.x * step[e].y + c0.y * step[e].x);
+              }
+            }
+            if (inter) {
 #pragma unroll
               for (int e = 0; e < VEC; e += 2) {
-                const float2 c = cs[u][e >> 1];
+                const float2 c = cs[e >> 1];
                 const float v0 = x[u][e], v1 = x[u][e + 1];
                 x[u][e] = v0 * c.x - v1 * c.y;
                 x[u][e + 1] = v0 * c.y + v1 * c.x;
@@ -488,12 +539,11 @@ __global__ void __launch_bounds__(384, 1)
             } else {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) {
-                const float other = __shfl_xor_sync(0xffffffffu, x[u][e], 16);
-                const float2 c = cs[u][e];
-                x[u][e] = (d0 + e < HD / 2) ? x[u][e] * c.x - other * c.y : other * c.y + x[u][e] * c.x;
+                const float2 c = cs[e];
+                x[u][e] = (d0 + e < HD / 2) ? x[u][e] * c.x - other[k][e] * c.y : other[k][e] * c.y + x[u][e] * c.x;
               }
             }
-            const int row = (warp & 3) * 32 + rb + u;
+            const int row = row0 + u;
             const uint32_t addr = swz128(q_tile + (d0 >> 6) * Cfg::kHalfBytes, row, (d0 & 63) >> 3) + (d0 & 7) * 2;
             if constexpr (VEC == 4) {
               asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(pack_half2(x[u][0], x[u][1])),
