@@ -95,3 +95,34 @@ def test_product_package_never_imports_the_oracle():
                 src = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in src and "from oracle" not in src, f
                 assert "liboracle" not in src and "tensor_ref" not in src, f
+
+
+def test_struct_layouts_match_the_headers(tmp_path):
+    """Every struct that crosses the C ABI: field offsets and sizes as gcc lays out the header's definition
+    against the ctypes mirror the tests and the benchmark use."""
+    import shutil
+    import subprocess
+    from hippo_leap_b200 import backend, dense
+    gcc = shutil.which("gcc") or "/usr/bin/gcc"
+    pairs = {"hl_attn_shape": _lib.AttnShapeC, "hl_view": _lib.ViewC, "hl_hparams": backend.HParamsC,
+             "hl_standin_weights": backend.WeightsC, "hl_kv_cache": backend.KvCacheC,
+             "hl_dense_hparams": dense.DenseHParamsC, "hl_dense_weights": dense.DenseWeightsC}
+    inc = os.path.join(os.path.dirname(__file__), "..", "include")
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "hl_b200.h"', '#include "hl_backend.h"', 'int main(void) {']
+    for cname, cls in pairs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-I", inc, str(src), "-o", str(exe)], check=True)
+    got = {}
+    for ln in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines():
+        c, f, v = ln.split()
+        got[(c, f)] = int(v)
+    for cname, cls in pairs.items():
+        assert got[(cname, "size")] == C.sizeof(cls), cname
+        for fname, _ in cls._fields_:
+            assert got[(cname, fname)] == getattr(cls, fname).offset, (cname, fname)
