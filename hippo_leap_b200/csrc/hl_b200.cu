@@ -21,6 +21,7 @@
 #include "host_common.h"
 #include "kv_append.cuh"
 #include "linear_f16.cuh"
+#include "linear_f16_pair.cuh"
 #include "linear_gemv.cuh"
 
 using namespace hl;
@@ -794,19 +795,38 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
   } else {
     if ((lda & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
       return hl_fail(ctx, HL_ERR_ALIGN, "linear: A and W need 16-byte aligned bases and row strides (multiples of 8 halfs)");
-    using Cfg = LinearGemmCfg;
-    static bool configured[16] = {};
-    if (!configured[ctx->device & 15]) {
-      HL_CUDA(ctx, cudaFuncSetAttribute(linear_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-      configured[ctx->device & 15] = true;
+    static const bool no_pair = getenv("HL_B200_GEMM_NO_PAIR") != nullptr;
+    if (M >= 512 && !no_pair) {
+      // 256 x 256 tiles on SM pairs (linear_f16_pair.cuh)
+      using Cfg = LinearPairCfg;
+      static bool configured2[16] = {};
+      if (!configured2[ctx->device & 15]) {
+        HL_CUDA(ctx, cudaFuncSetAttribute(linear_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        configured2[ctx->device & 15] = true;
+      }
+      CUtensorMap a_map, w_map;
+      rc = make_map_2d(ctx, &a_map, a, M, K, lda, Cfg::BM);
+      if (rc == HL_OK) rc = make_map_2d(ctx, &w_map, w, N, K, ldw, Cfg::BNH);
+      if (rc != HL_OK) return rc;
+      const int n_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+      const int max_pairs = ctx->n_sm / 2;
+      const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;
+      linear_gemm_pair_kernel<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(a_map, w_map, g);
+    } else {
+      using Cfg = LinearGemmCfg;
+      static bool configured[16] = {};
+      if (!configured[ctx->device & 15]) {
+        HL_CUDA(ctx, cudaFuncSetAttribute(linear_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        configured[ctx->device & 15] = true;
+      }
+      CUtensorMap a_map, w_map;
+      rc = make_map_2d(ctx, &a_map, a, M, K, lda, Cfg::BM);
+      if (rc == HL_OK) rc = make_map_2d(ctx, &w_map, w, N, K, ldw, Cfg::BN);
+      if (rc != HL_OK) return rc;
+      const int n_tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + Cfg::BN - 1) / Cfg::BN);
+      const int grid = n_tiles < ctx->n_sm ? n_tiles : ctx->n_sm;
+      linear_gemm_kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(a_map, w_map, g);
     }
-    CUtensorMap a_map, w_map;
-    rc = make_map_2d(ctx, &a_map, a, M, K, lda, Cfg::BM);
-    if (rc == HL_OK) rc = make_map_2d(ctx, &w_map, w, N, K, ldw, Cfg::BN);
-    if (rc != HL_OK) return rc;
-    const int n_tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + Cfg::BN - 1) / Cfg::BN);
-    const int grid = n_tiles < ctx->n_sm ? n_tiles : ctx->n_sm;
-    linear_gemm_kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(a_map, w_map, g);
   }
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());

@@ -39,6 +39,17 @@ def test_gemv_against_oracle_matmul(hl_ctx, M, N, K):
     _check(hl_ctx, M, N, K, resid=True, out_dtype=torch.float32)
 
 
+@pytest.mark.parametrize("M,N,K,resid,dt", [
+    (512, 256, 64, False, torch.float32),       # one pair tile per 256 columns, a single K step
+    (600, 300, 200, True, torch.float32),       # ragged in M (the peer CTA's last rows), N and K
+    (4096, 1024, 512, False, torch.float16),    # more tiles than SM pairs: both accumulators, ring wrap-around
+    (769, 513, 1032, True, torch.float16),      # second CTA of the last pair row holds a single live row
+])
+def test_pair_gemm_against_oracle_matmul(hl_ctx, M, N, K, resid, dt):
+    """M >= 512 runs on SM pairs (256 x 256 tiles, tcgen05 cta_group::2)."""
+    _check(hl_ctx, M, N, K, resid=resid, out_dtype=dt, seed=M + N)
+
+
 def test_residual_and_fp16_output(hl_ctx):
     _check(hl_ctx, 384, 512, 256, resid=True, out_dtype=torch.float32, seed=3)
     _check(hl_ctx, 384, 512, 256, resid=False, out_dtype=torch.float16, seed=4)
