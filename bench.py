@@ -225,6 +225,10 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
         q = torch.randn((S, cfg.n_head, cfg.head_dim), generator=gen, device=device)
         k = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
         v = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        if cfg.bf16_range:    # values a bf16 model would produce, still handed over as float32
+            q, k, v = (x.bfloat16().float() for x in (q, k, v))
+        if cfg.fp16_inputs:   # activations arrive as fp16
+            q, k, v = (x.half() for x in (q, k, v))
         out = torch.empty((S, cfg.n_head, cfg.head_dim), dtype=torch.float16, device=device)
         ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
         n = 2 if quick else 5
@@ -235,7 +239,8 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
         fl = synth.prefill_flops(cfg.n_head, cfg.head_dim, S)
         tf = fl / (ms * 1e-3) / 1e12
         res[f"config{ci}_prefill"] = {
-            "workload": f"{cfg.name}: causal prefill of {S} tokens, one layer", "ms_attn": ms, "ms_kv_append": ms_app,
+            "workload": f"{cfg.name}: causal prefill of {S} tokens, one layer, "
+                        f"{'fp16' if cfg.fp16_inputs else 'float32'} Q/K/V in, fp16 out", "ms_attn": ms, "ms_kv_append": ms_app,
             "tflops": tf, "frac_of_tensor_peak": tf / peaks["tflops"], "peak_tflops": peaks["tflops"],
             "peak_src": peaks["src"], "flops": fl}
         kv.destroy()
@@ -425,6 +430,8 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
     q = torch.randn((S, hq_l, cfg.head_dim), generator=gen, device=device)
     k = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
     v = torch.randn((S, hkv_l, cfg.head_dim), generator=gen, device=device)
+    if cfg.fp16_inputs:
+        q, k, v = (x.half() for x in (q, k, v))
     ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
     results = {}
     fused = sharding.FusedHeadShardedPrefill(ctx, kv, shape, S, cfg.n_head, device)

@@ -27,6 +27,7 @@ class AttnConfig:
     qk_norm: bool = False
     rms_eps: float = 1e-6
     bf16_range: bool = False  # activations rounded to bf16 before use
+    fp16_inputs: bool = False  # Q / K / V handed to the kernels as fp16 (config 5), float32 otherwise
     batch: int = 1            # concurrent sequences (batched decode)
     ctx_range: tuple = (0, 0)
     block_tokens: int = 16
@@ -49,7 +50,7 @@ CONFIGS = {
                   rms_eps=1e-6, bf16_range=True, seed=2),
     4: AttnConfig("llama-3-8b-batched-decode", 32, 8, 128, 5e5, layers=1, batch=64,
                   ctx_range=(512, 8192), block_tokens=16, seed=3),
-    5: AttnConfig("70b-class-long-prefill", 64, 8, 128, 5e5, layers=1, prefill=32768, seed=4),
+    5: AttnConfig("70b-class-long-prefill", 64, 8, 128, 5e5, layers=1, prefill=32768, fp16_inputs=True, seed=4),
 }
 
 

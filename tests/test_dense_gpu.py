@@ -15,7 +15,9 @@ pytestmark = pytest.mark.gpu
 
 
 class OracleDense:
-    def __init__(self, m: D.DenseModel, max_len: int, mirror_fp16: bool):
+    def __init__(self, m: D.DenseModel, max_len: int, mirror_fp16: bool, matmul=None):
+        # matmul: the oracle's triple loop (tensor.nim:63-81) unless a test at large widths passes a faster stand-in
+        self.mm = matmul or oracle.matmul
         hp = m.hparams
         self.m, self.hp, self.mirror = m, hp, mirror_fp16
         th = oracle.theta_table(hp.ropeDim or hp.headDim, hp.ropeFreqBase)
@@ -34,22 +36,22 @@ class OracleDense:
         x = w["tok_emb"][toks].astype(np.float32)
         for l in range(hp.nLayer):
             xn = self.r(oracle.rmsnorm(x, w["attn_norm"][l], hp.rmsEps))
-            q = oracle.matmul(xn, t["wq"][l]).reshape(n, hp.nHead, hp.headDim)
-            k = oracle.matmul(xn, t["wk"][l]).reshape(n, hp.nHeadKv, hp.headDim)
-            v = oracle.matmul(xn, t["wv"][l]).reshape(n, hp.nHeadKv, hp.headDim)
+            q = self.mm(xn, t["wq"][l]).reshape(n, hp.nHead, hp.headDim)
+            k = self.mm(xn, t["wk"][l]).reshape(n, hp.nHeadKv, hp.headDim)
+            v = self.mm(xn, t["wv"][l]).reshape(n, hp.nHeadKv, hp.headDim)
             o = oracle.attn_forward(q, k, v, self.caches[l], theta=self.theta, rope_mode=hp.ropeMode,
                                     q_norm_w=None if w["q_norm"] is None else w["q_norm"][l],
                                     k_norm_w=None if w["k_norm"] is None else w["k_norm"][l], eps=hp.rmsEps,
                                     kv_fp16=self.mirror)
             o = self.r(o.reshape(n, -1))
-            x = (x + oracle.matmul(o, t["wo"][l])).astype(np.float32)
+            x = (x + self.mm(o, t["wo"][l])).astype(np.float32)
             xn = self.r(oracle.rmsnorm(x, w["ffn_norm"][l], hp.rmsEps))
-            g = self.r(oracle.matmul(xn, t["w_gate"][l]))
-            u = self.r(oracle.matmul(xn, t["w_up"][l]))
+            g = self.r(self.mm(xn, t["w_gate"][l]))
+            u = self.r(self.mm(xn, t["w_up"][l]))
             h = self.r((g / (1.0 + np.exp(-g))).astype(np.float32) * u)  # silu(x) = x / (1 + exp(-x)), tensor.nim silu
-            x = (x + oracle.matmul(h, t["w_down"][l])).astype(np.float32)
+            x = (x + self.mm(h, t["w_down"][l])).astype(np.float32)
         xn = self.r(oracle.rmsnorm(x[-1:], w["out_norm"], hp.rmsEps))
-        return oracle.matmul(xn, t["w_out"])
+        return self.mm(xn, t["w_out"])
 
 
 CASES = {
@@ -106,6 +108,39 @@ def test_dense_model_against_oracle(name, prompt_len, graph):
                 assert ms > 0
             assert cache.curLen == prompt_len + step + 1
         assert cache.curLen <= max_len
+    finally:
+        D.unloadModelBackend()
+
+
+def test_dense_llama32_1b_dimensions_one_layer():
+    """One layer at the real Llama-3.2-1B widths (n_emb 2048, n_ffn 8192, 32 / 8 heads of 64, llama3-scaled theta) and
+    a 32000-entry vocabulary: the SM-pair GEMM on the 520-token prompt, the split-K decode projections (K = 8192) and
+    the two-stage argmax run at the sizes the benchmark uses.  At these widths the oracle's scalar triple loop takes
+    minutes, so the same layer stack is evaluated with a float64 numpy contraction rounded to float32 (the small cases
+    above pin the C oracle itself)."""
+    hp = D.DenseHParams(nVocab=32000, nEmb=2048, nLayer=1, nFfn=8192, nHead=32, nHeadKv=8, headDim=64,
+                        ropeFreqBase=500000.0, rmsEps=1e-5, ropeMode=hl.HL_ROPE_SPLIT_HALF, llama3Scaling=True)
+    m = D.random_dense_model(hp, 31)
+    prompt = np.random.Generator(np.random.PCG64([31, 1])).integers(0, hp.nVocab, 520).astype(np.int32)
+    max_len = 528
+    cache = D.initKvCache(hp, max_len)
+    D.loadModelBackend(m, hp)
+    ref = OracleDense(m, max_len, True, matmul=lambda a, b: (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+    try:
+        logits = D.forwardPrefill(m, prompt, cache)
+        want = ref.forward(prompt)
+        scale = float(np.abs(want).max())
+        assert_parity(logits, want, "prefill logits", max_abs_tol=3e-3 * scale, rel_l2_tol=1.5e-3)
+        tok = D.argmaxLast(want, hp.nVocab)
+        for step in range(3):
+            got_tok, ms = D.forwardDecodeTokenTimed(m, tok, cache)
+            want = ref.forward([tok])
+            top2 = np.sort(want[0])[-2:]
+            tok = D.argmaxLast(want, hp.nVocab)
+            assert got_tok == tok or top2[1] - top2[0] <= 1e-2 * float(np.abs(want).max()), f"step {step}"
+        logits = D.forwardDecode(m, tok, cache)
+        want = ref.forward([tok])
+        assert_parity(logits, want, "decode logits", max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
     finally:
         D.unloadModelBackend()
 
