@@ -208,12 +208,9 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     s.q_norm_w = d.q_norm ? d.q_norm + static_cast<size_t>(l) * hd : nullptr;
     s.k_norm_w = d.k_norm ? d.k_norm + static_cast<size_t>(l) * hd : nullptr;
     if (fused) {
-      // the attention kernels that follow leave HBM nearly idle: have this layer's gate|up weights (wo follows them
-      // through its own prefetch) on their way into L2 meanwhile
       D_TRY(hl_linear_decode_fused(d.ctx, 1, 0, d.x, E, d.attn_norm + static_cast<size_t>(l) * E, hp.rms_eps,
                                    d.wqkv + static_cast<size_t>(l) * qkvd * E, E, d.qkv, HL_DTYPE_F32, qkvd, nullptr, 0, n,
-                                   qkvd, E, d.wgu + static_cast<size_t>(l) * 2 * F * E,
-                                   static_cast<int64_t>(2) * F * E * sizeof(__half)));
+                                   qkvd, E));
     } else {
       rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.attn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
       d.ctx->launches += 1;

@@ -718,8 +718,7 @@ static int32_t launch_gemv_fused(hl_ctx* ctx, GemvArgs p) {
 
 int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const void* a, int64_t lda, const float* norm_w,
                                float eps, const void* w, int64_t ldw, void* out, int32_t out_dtype, int64_t ldo,
-                               const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K, const void* hint,
-                               int64_t hint_bytes) {
+                               const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K) {
   if (!ctx) return HL_ERR_ARG;
   if (!a || !w || !out || (mode == kGemvRmsNorm && !norm_w)) return hl_fail(ctx, HL_ERR_ARG, "decode projection: null pointer");
   if (M <= 0 || M > 4 || N <= 0 || K <= 0 || (K & 7) || (ldw & 7) || ldw >= (1 << 28) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -738,11 +737,6 @@ int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const 
   p.eps = eps;
   p.mode = mode;
   p.swiglu = swiglu;
-  static const bool no_hint = getenv("HL_B200_NO_L2_HINT") != nullptr;
-  if (hint && hint_bytes >= 16 && !no_hint && (reinterpret_cast<uintptr_t>(hint) & 15) == 0) {
-    p.hint = hint;
-    p.hint_bytes = hint_bytes & ~static_cast<int64_t>(15);
-  }
   p.g.w = static_cast<const __half*>(w);
   p.g.out = out;
   p.g.resid = resid;

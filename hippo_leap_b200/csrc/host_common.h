@@ -45,11 +45,9 @@ int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...);
 
 // Decode projection (linear_gemv.cuh), 1 <= M <= 4.  mode 0: a = fp16 rows; mode 1: a = fp32 rows (lda in floats),
 // RMSNorm with norm_w fused in front.  swiglu != 0: W rows interleave gate / up, out[M][N / 2] = fp16 silu(gate) * up.
-// hint / hint_bytes: weights a later kernel will stream, requested into L2 as this kernel finishes.
 int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const void* a, int64_t lda, const float* norm_w,
                                float eps, const void* w, int64_t ldw, void* out, int32_t out_dtype, int64_t ldo,
-                               const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K,
-                               const void* hint = nullptr, int64_t hint_bytes = 0);
+                               const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K);
 
 #define HL_CUDA(ctx, expr)                                                                   \
   do {                                                                                       \

@@ -16,9 +16,6 @@
 //   * Launched with programmatic stream serialisation: a block first asks L2 to prefetch its weight rows
 //     (which no kernel writes), lets the next kernel in the stream start, and only then waits for the kernels before
 //     it (griddepcontrol.wait) and reads activations.  A chain of these keeps HBM busy across kernel boundaries.
-//   * Optional hint: a range of weights that a later kernel of the step will read (the output and gate|up
-//     projections, while the attention kernels in between leave HBM idle).  Every warp asks L2 to prefetch its share
-//     once its own loads are done.
 //   * KS > 1 (few output rows): the KS slice warps of a row group sit in one block; partial sums meet in shared
 //     memory and are added in slice order, so the result does not depend on scheduling.
 #pragma once
@@ -39,8 +36,6 @@ struct GemvArgs {
   int64_t ldx;
   float eps;
   int32_t mode, swiglu, ks, kslice;  // kslice: multiple of 256
-  const void* hint;      // optional: weights some LATER kernel will stream; requested into L2 when this one is done
-  int64_t hint_bytes;    // with its own (multiple of 16)
 };
 
 template <int MAXM, int R>
@@ -147,16 +142,6 @@ __global__ void __launch_bounds__(256, MAXM == 1 ? 4 : 2) linear_gemv_fused_kern
           }
         }
       }
-    }
-  }
-  if (p.hint_bytes > 0 && lane == 0) {
-    const int64_t n_warps = static_cast<int64_t>(gridDim.x) * 8;
-    const int64_t per = ((p.hint_bytes + n_warps - 1) / n_warps + 15) & ~static_cast<int64_t>(15);
-    const int64_t beg = gw * per, end = min(p.hint_bytes, beg + per);
-    for (int64_t o = beg; o < end; o += 8192) {
-      const int64_t left = end - o;
-      const uint32_t sz = static_cast<uint32_t>(left < 8192 ? left : 8192);
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(p.hint) + o), "r"(sz) : "memory");
     }
   }
 #pragma unroll
