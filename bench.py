@@ -402,6 +402,29 @@ def extra_dense_model(torch, device_index, prefill=2048, decode_steps=64):
                    "decode_gpu_ms_per_token": gpu_ms / decode_steps,
                    "decode_weight_gbs": weight_bytes / (gpu_ms / decode_steps * 1e-3) / 1e9,
                    "weight_bytes": weight_bytes}
+        # several sequences decoded together from one shared page pool: every weight is read once per step for all of them
+        batched = {}
+        pool = D.DecodeBatch(m, 64, 512 + 40)
+        try:
+            short = prompt[:512]
+            for s in range(64):
+                pool.prefill(s, short)
+            for nb in (1, 4, 16, 64):
+                ids = np.arange(nb, dtype=np.int32)
+                toks = np.full(nb, 11, np.int32)
+                for _ in range(2):
+                    toks, _ = pool.decode(ids, toks)
+                gpu_ms, steps = 0.0, 8
+                t0 = time.perf_counter()
+                for _ in range(steps):
+                    toks, _, ms = pool.decode(ids, toks, timed=True)
+                    gpu_ms += ms
+                wall = time.perf_counter() - t0
+                batched[f"{nb}_sequences"] = {"ms_per_step": wall * 1e3 / steps, "gpu_ms_per_step": gpu_ms / steps,
+                                              "tok_per_s": nb * steps / wall}
+        finally:
+            pool.close()
+        res["batched_decode_ctx512"] = batched
         return res
     finally:
         D.freeKvCache(cache)

@@ -150,8 +150,12 @@ __device__ __forceinline__ void argmax_block_reduce(float& best, int& idx) {
     for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) argmax_take(best, idx, bv[w], bi[w]);
 }
 
+// blockIdx.y: the row of logits (one per sequence of a batched step)
 __global__ void __launch_bounds__(256) argmax_partial(const float* __restrict__ logits, int n, float* __restrict__ cand_v,
                                                       int32_t* __restrict__ cand_i) {
+  logits += static_cast<int64_t>(blockIdx.y) * n;
+  cand_v += blockIdx.y * kArgmaxBlocks;
+  cand_i += blockIdx.y * kArgmaxBlocks;
   const int per = (n + gridDim.x - 1) / gridDim.x;
   const int beg = blockIdx.x * per, end = min(n, beg + per);
   float best = -INFINITY;
@@ -166,10 +170,10 @@ __global__ void __launch_bounds__(256) argmax_partial(const float* __restrict__ 
 
 __global__ void __launch_bounds__(kArgmaxBlocks) argmax_final(const float* __restrict__ cand_v,
                                                               const int32_t* __restrict__ cand_i, int32_t* __restrict__ out) {
-  float best = cand_v[threadIdx.x];
-  int idx = cand_i[threadIdx.x];
+  float best = cand_v[blockIdx.x * kArgmaxBlocks + threadIdx.x];
+  int idx = cand_i[blockIdx.x * kArgmaxBlocks + threadIdx.x];
   argmax_block_reduce(best, idx);
-  if (threadIdx.x == 0) *out = idx == 0x7fffffff ? 0 : idx;
+  if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
 }
 
 void launch_argmax(cudaStream_t st);
@@ -177,10 +181,29 @@ void launch_argmax(cudaStream_t st);
 // One forward over n tokens starting at position pos0; decode is n == 1.  `grid_ctx` sizes the decode grid and its
 // scratch (>= the real context); with `from_pinned` the token id and the context length come from the pinned step
 // record through copy nodes, so that a captured graph of the sequence can be replayed for every token.
-int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bool decode, int grid_ctx = 0,
-                bool from_pinned = false) {
+//
+// `bd` switches to a decode step over n DIFFERENT sequences of a shared pool (continuous batching): row i is one new
+// token of the sequence whose context length (after the append) is bd->ctx_lens_d[i] and whose pages are row i of
+// bd->tables_d; logits of all n rows go to bd->logits_d.
+struct BatchDecode {
+  hl_kv* kv;
+  const int32_t* ctx_lens_d;  // [n]
+  const int32_t* tables_d;    // [n][table_len]
+  int table_len, max_ctx;
+  float* logits_d;            // [n][n_vocab]
+};
+struct KvRef {
+  hl_kv* kv;
+  const int32_t* table;  // block table of the one sequence (prefill / single-sequence decode)
+  int table_len;
+};
+
+KvRef ref_of(const hl_kv_cache* cache) { return KvRef{static_cast<hl_kv*>(cache->gpu_cache), d.table_d, d.table_len}; }
+
+int32_t forward(const int32_t* tokens_h, int n, int pos0, KvRef ref, bool decode, int grid_ctx = 0,
+                bool from_pinned = false, const BatchDecode* bd = nullptr) {
   using namespace hl;
-  hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
+  hl_kv* kv = bd ? bd->kv : ref.kv;
   const hl_dense_hparams& hp = d.hp;
   const int E = hp.n_emb, F = hp.n_ffn, hd = hp.head_dim, qd = hp.n_head * hd, kd = hp.n_head_kv * hd, qkvd = qd + 2 * kd;
   D_CUDA(cudaSetDevice(d.device));
@@ -191,7 +214,7 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     D_CUDA(cudaMemcpyAsync(d.ctx_len_d, &d.pinned[5], sizeof(int32_t), cudaMemcpyHostToDevice, st));
   } else {
     D_CUDA(cudaMemcpyAsync(d.tokens_d, tokens_h, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-    if (decode) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
+    if (decode && !bd) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
   }
   if (grid_ctx < pos0 + 1) grid_ctx = pos0 + 1;
   const bool fused = n <= 4;  // decode-sized: RMSNorm and SwiGLU run as prologues of the projection that follows them
@@ -219,12 +242,16 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     }
     hl_view qv{d.qkv, HL_DTYPE_F32, qkvd, hd, 1}, kvw{d.qkv + qd, HL_DTYPE_F32, qkvd, hd, 1},
         vv{d.qkv + qd + kd, HL_DTYPE_F32, qkvd, hd, 1}, ov{d.attn, HL_DTYPE_F16, qd, hd, 1};
-    if (decode) {
-      D_TRY(hl_b200_kv_append_batch(d.ctx, kv, l, &s, &kvw, &vv, 1, d.ctx_len_d, d.table_d, d.table_len));
-      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, 1, d.ctx_len_d, grid_ctx, d.table_d, d.table_len, &ov, nullptr));
+    if (bd) {
+      D_TRY(hl_b200_kv_append_batch(d.ctx, kv, l, &s, &kvw, &vv, n, bd->ctx_lens_d, bd->tables_d, bd->table_len));
+      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, n, bd->ctx_lens_d, bd->max_ctx, bd->tables_d, bd->table_len, &ov,
+                                nullptr));
+    } else if (decode) {
+      D_TRY(hl_b200_kv_append_batch(d.ctx, kv, l, &s, &kvw, &vv, 1, d.ctx_len_d, ref.table, ref.table_len));
+      D_TRY(hl_b200_attn_decode(d.ctx, kv, l, &s, &qv, 1, d.ctx_len_d, grid_ctx, ref.table, ref.table_len, &ov, nullptr));
     } else {
-      D_TRY(hl_b200_kv_append_seq(d.ctx, kv, l, &s, &kvw, &vv, n, pos0, d.table_d, d.table_len));
-      D_TRY(hl_b200_attn_prefill(d.ctx, kv, l, &s, &qv, n, pos0, d.table_d, d.table_len, &ov, nullptr));
+      D_TRY(hl_b200_kv_append_seq(d.ctx, kv, l, &s, &kvw, &vv, n, pos0, ref.table, ref.table_len));
+      D_TRY(hl_b200_attn_prefill(d.ctx, kv, l, &s, &qv, n, pos0, ref.table, ref.table_len, &ov, nullptr));
     }
     // x += attn . Wo^T   (output projection + residual, naive.nim:4079-4080)
     D_TRY(hl_b200_linear_f16(d.ctx, d.attn, qd, d.wo + static_cast<size_t>(l) * E * qd, qd, d.x, HL_DTYPE_F32, E, d.x, E, n,
@@ -246,6 +273,20 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
       D_TRY(hl_b200_linear_f16(d.ctx, d.h, F, d.wdown + static_cast<size_t>(l) * E * F, F, d.x, HL_DTYPE_F32, E, d.x, E, n, E,
                                F, nullptr));
     }
+  }
+  if (bd) {
+    // final norm + vocabulary projection of every row (each is the last position of its sequence)
+    if (fused) {
+      D_TRY(hl_linear_decode_fused(d.ctx, 1, 0, d.x, E, d.out_norm, hp.rms_eps, d.wout, E, bd->logits_d, HL_DTYPE_F32,
+                                   hp.n_vocab, nullptr, 0, n, hp.n_vocab, E));
+    } else {
+      rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.out_norm, E, hp.rms_eps, d.xn);
+      d.ctx->launches += 1;
+      D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wout, E, bd->logits_d, HL_DTYPE_F32, hp.n_vocab, nullptr, 0, n, hp.n_vocab,
+                               E, nullptr));
+    }
+    D_CUDA(cudaGetLastError());
+    return HL_OK;
   }
   // final norm + vocabulary projection of the LAST position only
   D_TRY(hl_linear_decode_fused(d.ctx, 1, 0, d.x + static_cast<size_t>(n - 1) * E, E, d.out_norm, hp.rms_eps, d.wout, E, d.logits,
@@ -286,11 +327,11 @@ int32_t ensure_decode_graph(hl_kv_cache* cache) {
   cudaStream_t st = d.ctx->stream;
   // an uncaptured pass first: it configures kernels and grows every scratch buffer, so nothing allocates or
   // synchronises during capture; the first replay repeats it at the same position with the same values
-  D_PASS(forward(nullptr, 1, d.pinned[5] - 1, cache, true, cache->max_len, true));
+  D_PASS(forward(nullptr, 1, d.pinned[5] - 1, ref_of(cache), true, cache->max_len, true));
   D_CUDA(cudaStreamSynchronize(st));
   D_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
   const int64_t counted = d.ctx->launches;
-  int32_t rc = forward(nullptr, 1, d.pinned[5] - 1, cache, true, cache->max_len, true);
+  int32_t rc = forward(nullptr, 1, d.pinned[5] - 1, ref_of(cache), true, cache->max_len, true);
   if (rc == HL_OK) {
     launch_argmax(st);
     cudaMemcpyAsync(&d.pinned[2], d.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
@@ -340,6 +381,132 @@ int32_t decode_graph(int32_t token, hl_kv_cache* cache, float* logits_h, int32_t
 }
 
 }  // namespace
+
+// ---- several sequences in one shared page pool, decoded together (continuous batching hook) ----------------------
+struct hl_dense_batch {
+  hl_kv* kv = nullptr;
+  int max_seqs = 0, max_len = 0, nb = 0;
+  std::vector<int32_t> cur_len;        // tokens held per sequence
+  int32_t* tables_d = nullptr;         // [max_seqs][nb]: sequence s owns pages [s * nb, (s + 1) * nb)
+  int32_t* act_tables_d = nullptr;     // [max_seqs][nb]: rows of the sequences of the current step
+  int32_t* ctx_lens_d = nullptr;       // [max_seqs]
+  int32_t *next_d = nullptr, *cand_i = nullptr;
+  float *cand_v = nullptr, *logits_d = nullptr;  // [max_seqs][n_vocab]
+  int32_t* pinned = nullptr;           // [0..1] status, [2 ..] step inputs / next tokens
+};
+
+extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_dense_batch** out) {
+  if (!out) return dfail(HL_ERR_ARG, "null out");
+  *out = nullptr;
+  if (!d.loaded) return dfail(HL_ERR_ARG, "no model loaded (loadModelBackend)");
+  if (max_seqs <= 0 || max_seqs > 4096 || max_len <= 0) return dfail(HL_ERR_ARG, "max_seqs must be 1..4096 and max_len positive");
+  D_CUDA(cudaSetDevice(d.device));
+  hl_dense_batch* b = new hl_dense_batch();
+  b->max_seqs = max_seqs;
+  b->max_len = max_len;
+  b->nb = (max_len + 127) / 128;
+  b->cur_len.assign(max_seqs, 0);
+  const size_t nt = static_cast<size_t>(max_seqs) * b->nb, V = d.hp.n_vocab;
+  int32_t rc = hl_b200_kv_create(d.ctx, d.hp.n_layer, d.hp.n_head_kv, d.hp.head_dim, 128, static_cast<int32_t>(nt), &b->kv);
+  std::vector<int32_t> ident(nt);
+  for (size_t i = 0; i < nt; ++i) ident[i] = static_cast<int32_t>(i);
+  const bool ok = rc == HL_OK && cudaMalloc(&b->tables_d, nt * 4) == cudaSuccess &&
+                  cudaMemcpy(b->tables_d, ident.data(), nt * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+                  cudaMalloc(&b->act_tables_d, nt * 4) == cudaSuccess && cudaMalloc(&b->ctx_lens_d, max_seqs * 4) == cudaSuccess &&
+                  cudaMalloc(&b->next_d, max_seqs * 4) == cudaSuccess &&
+                  cudaMalloc(&b->cand_i, static_cast<size_t>(max_seqs) * kArgmaxBlocks * 4) == cudaSuccess &&
+                  cudaMalloc(&b->cand_v, static_cast<size_t>(max_seqs) * kArgmaxBlocks * 4) == cudaSuccess &&
+                  cudaMalloc(&b->logits_d, static_cast<size_t>(max_seqs) * V * 4) == cudaSuccess &&
+                  cudaMallocHost(&b->pinned, (2 + 2 * static_cast<size_t>(max_seqs) + nt) * 4) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    hl_dense_batch_destroy(b);
+    return rc != HL_OK ? dfail_ctx(rc, "hl_b200_kv_create") : dfail(HL_ERR_CUDA, "allocation of the batch state failed");
+  }
+  *out = b;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_batch_destroy(hl_dense_batch* b) {
+  if (!b) return HL_OK;
+  if (d.ctx) {
+    cudaSetDevice(d.device);
+    cudaStreamSynchronize(d.ctx->stream);
+    if (b->kv) hl_b200_kv_destroy(d.ctx, b->kv);
+  }
+  for (int32_t** p : {&b->tables_d, &b->act_tables_d, &b->ctx_lens_d, &b->next_d, &b->cand_i})
+    if (*p) cudaFree(*p);
+  for (float** p : {&b->cand_v, &b->logits_d})
+    if (*p) cudaFree(*p);
+  if (b->pinned) cudaFreeHost(b->pinned);
+  delete b;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_batch_seq_len(const hl_dense_batch* b, int32_t seq) {
+  return (b && seq >= 0 && seq < b->max_seqs) ? b->cur_len[seq] : -1;
+}
+
+extern "C" int32_t hl_dense_batch_prefill(hl_dense_batch* b, int32_t seq, const int32_t* tokens_h, int32_t n, int32_t start_pos,
+                                          float* logits_h) {
+  if (!b || !d.loaded) return dfail(HL_ERR_ARG, "no model loaded or null batch");
+  if (seq < 0 || seq >= b->max_seqs) return dfail(HL_ERR_ARG, "sequence index out of range");
+  if (!tokens_h || !logits_h) return dfail(HL_ERR_ARG, "null argument");
+  if (n <= 0) return dfail(HL_ERR_ARG, "prefill requires at least one token");
+  if (start_pos < 0 || start_pos > b->cur_len[seq]) return dfail(HL_ERR_ARG, "start_pos must lie within what the sequence already holds");
+  if (static_cast<int64_t>(start_pos) + n > b->max_len) return dfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
+  D_PASS(forward(tokens_h, n, start_pos, KvRef{b->kv, b->tables_d + static_cast<size_t>(seq) * b->nb, b->nb}, false));
+  D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
+  D_PASS(finish());
+  b->cur_len[seq] = start_pos + n;
+  return HL_OK;
+}
+
+extern "C" int32_t hl_dense_batch_decode(hl_dense_batch* b, const int32_t* seq_ids_h, const int32_t* tokens_h, int32_t n_active,
+                                         int32_t* next_tokens_h, float* logits_h, float* gpu_ms) {
+  if (!b || !d.loaded) return dfail(HL_ERR_ARG, "no model loaded or null batch");
+  if (!seq_ids_h || !tokens_h || (!next_tokens_h && !logits_h)) return dfail(HL_ERR_ARG, "null argument");
+  if (n_active <= 0 || n_active > b->max_seqs) return dfail(HL_ERR_ARG, "n_active must be 1..max_seqs");
+  D_CUDA(cudaSetDevice(d.device));
+  const int n = n_active, nb = b->nb;
+  int32_t* ctx_h = b->pinned + 2 + b->max_seqs;        // [n]
+  int32_t* tab_h = b->pinned + 2 + 2 * b->max_seqs;    // [n][nb]
+  std::vector<char> seen(b->max_seqs, 0);
+  int max_ctx = 0;
+  for (int i = 0; i < n; ++i) {
+    const int s = seq_ids_h[i];
+    if (s < 0 || s >= b->max_seqs) return dfail(HL_ERR_ARG, "sequence index out of range");
+    if (seen[s]) return dfail(HL_ERR_ARG, "a sequence appears twice in one decode step");
+    seen[s] = 1;
+    if (b->cur_len[s] >= b->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
+    ctx_h[i] = b->cur_len[s] + 1;
+    max_ctx = ctx_h[i] > max_ctx ? ctx_h[i] : max_ctx;
+    for (int j = 0; j < nb; ++j) tab_h[static_cast<size_t>(i) * nb + j] = s * nb + j;
+  }
+  cudaStream_t st = d.ctx->stream;
+  D_CUDA(cudaStreamSynchronize(st));  // the pinned step record of the previous call has been consumed
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
+  D_CUDA(cudaMemcpyAsync(b->ctx_lens_d, ctx_h, n * 4, cudaMemcpyHostToDevice, st));
+  D_CUDA(cudaMemcpyAsync(b->act_tables_d, tab_h, static_cast<size_t>(n) * nb * 4, cudaMemcpyHostToDevice, st));
+  BatchDecode bd{b->kv, b->ctx_lens_d, b->act_tables_d, nb, max_ctx, b->logits_d};
+  D_PASS(forward(tokens_h, n, 0, KvRef{}, true, 0, false, &bd));
+  if (next_tokens_h) {
+    argmax_partial<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(b->logits_d, d.hp.n_vocab, b->cand_v, b->cand_i);
+    argmax_final<<<n, kArgmaxBlocks, 0, st>>>(b->cand_v, b->cand_i, b->next_d);
+    d.ctx->launches += 2;
+  }
+  if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, st));
+  if (next_tokens_h) D_CUDA(cudaMemcpyAsync(b->pinned + 2, b->next_d, n * 4, cudaMemcpyDeviceToHost, st));
+  if (logits_h)
+    D_CUDA(cudaMemcpyAsync(logits_h, b->logits_d, static_cast<size_t>(n) * d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, st));
+  D_PASS(finish());
+  if (gpu_ms) D_CUDA(cudaEventElapsedTime(gpu_ms, d.e0, d.e1));
+  for (int i = 0; i < n; ++i) {
+    if (next_tokens_h) next_tokens_h[i] = b->pinned[2 + i];
+    b->cur_len[seq_ids_h[i]] += 1;
+  }
+  return HL_OK;
+}
 
 extern "C" int32_t hl_dense_set_decode_graph(int32_t enabled) {
   d.use_graph = enabled != 0;
@@ -470,7 +637,7 @@ extern "C" int32_t hl_dense_forward_prefill(const int32_t* tokens_h, int32_t n, 
   if (!tokens_h || !logits_h) return dfail(HL_ERR_ARG, "null argument");
   if (n <= 0) return dfail(HL_ERR_ARG, "prefill requires at least one token");
   if (n > cache->max_len) return dfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
-  D_PASS(forward(tokens_h, n, 0, cache, false));
+  D_PASS(forward(tokens_h, n, 0, ref_of(cache), false));
   D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
   D_PASS(finish());
   cache->cur_len = n;
@@ -483,7 +650,7 @@ extern "C" int32_t hl_dense_forward_prefill_chunk(const int32_t* tokens_h, int32
   if (n <= 0) return dfail(HL_ERR_ARG, "prefill requires at least one token");
   if (cache->cur_len < 0) return dfail(HL_ERR_ARG, "negative cur_len");
   if (static_cast<int64_t>(cache->cur_len) + n > cache->max_len) return dfail(HL_ERR_CAPACITY, "prefill exceeds KV cache capacity");
-  D_PASS(forward(tokens_h, n, cache->cur_len, cache, false));
+  D_PASS(forward(tokens_h, n, cache->cur_len, ref_of(cache), false));
   D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
   D_PASS(finish());
   cache->cur_len += n;
@@ -495,7 +662,7 @@ extern "C" int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, fl
   if (!logits_h) return dfail(HL_ERR_ARG, "null logits");
   if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
   if (d.use_graph) return decode_graph(token, cache, logits_h, nullptr, nullptr);
-  D_PASS(forward(&token, 1, cache->cur_len, cache, true));
+  D_PASS(forward(&token, 1, cache->cur_len, ref_of(cache), true));
   D_CUDA(cudaMemcpyAsync(logits_h, d.logits, d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, d.ctx->stream));
   D_PASS(finish());
   cache->cur_len += 1;
@@ -508,7 +675,7 @@ extern "C" int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cach
   if (cache->cur_len >= cache->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
   if (d.use_graph) return decode_graph(token, cache, nullptr, next_token, gpu_ms);
   if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, d.ctx->stream));
-  D_PASS(forward(&token, 1, cache->cur_len, cache, true));
+  D_PASS(forward(&token, 1, cache->cur_len, ref_of(cache), true));
   launch_argmax(d.ctx->stream);
   if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, d.ctx->stream));
   D_CUDA(cudaMemcpyAsync(&d.pinned[2], d.next_d, sizeof(int32_t), cudaMemcpyDeviceToHost, d.ctx->stream));

@@ -37,6 +37,11 @@ DENSE_SYMBOLS = {
     "hl_dense_forward_prefill_chunk": (_i32, [C.POINTER(_i32), _i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode": (_i32, [_i32, C.POINTER(KvCacheC), _f32p]),
     "hl_dense_forward_decode_token_timed": (_i32, [_i32, C.POINTER(KvCacheC), C.POINTER(_i32), _f32p]),
+    "hl_dense_batch_create": (_i32, [_i32, _i32, C.POINTER(C.c_void_p)]),
+    "hl_dense_batch_destroy": (_i32, [C.c_void_p]),
+    "hl_dense_batch_seq_len": (_i32, [C.c_void_p, _i32]),
+    "hl_dense_batch_prefill": (_i32, [C.c_void_p, _i32, C.POINTER(_i32), _i32, _i32, _f32p]),
+    "hl_dense_batch_decode": (_i32, [C.c_void_p, C.POINTER(_i32), C.POINTER(_i32), _i32, C.POINTER(_i32), _f32p, _f32p]),
     "hl_dense_set_decode_graph": (_i32, [_i32]),
     "hl_dense_last_error": (C.c_char_p, []),
 }
@@ -163,3 +168,41 @@ def setDecodeGraph(enabled: bool):
 
 def forwardDecodeToken(m: DenseModel, token: int, cache: KvCache) -> int:
     return forwardDecodeTokenTimed(m, token, cache)[0]
+
+
+class DecodeBatch:
+    """Several sequences of the loaded model in one shared page pool, decoded together (hl_dense_batch_*): a
+    continuous-batching hook.  The reference serves one sequence per process."""
+
+    def __init__(self, m: DenseModel, max_seqs: int, max_len: int):
+        self.n_vocab = m.hparams.nVocab
+        self.handle = C.c_void_p()
+        _check(_lib().hl_dense_batch_create(max_seqs, max_len, C.byref(self.handle)))
+
+    def close(self):
+        if self.handle:
+            _lib().hl_dense_batch_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def seq_len(self, seq: int) -> int:
+        return _lib().hl_dense_batch_seq_len(self.handle, seq)
+
+    def prefill(self, seq: int, tokens, start_pos: int = 0) -> np.ndarray:
+        toks = np.ascontiguousarray(tokens, np.int32)
+        logits = np.empty((1, self.n_vocab), np.float32)
+        _check(_lib().hl_dense_batch_prefill(self.handle, seq, toks.ctypes.data_as(C.POINTER(_i32)), toks.size, start_pos,
+                                             logits.ctypes.data_as(_f32p)))
+        return logits
+
+    def decode(self, seq_ids, tokens, want_logits: bool = False, timed: bool = False):
+        """One step for the given sequences.  Returns (next_tokens [n], logits [n, nVocab] or None[, gpu ms])."""
+        ids = np.ascontiguousarray(seq_ids, np.int32)
+        toks = np.ascontiguousarray(tokens, np.int32)
+        assert ids.shape == toks.shape and ids.ndim == 1
+        nxt = np.empty(ids.size, np.int32)
+        logits = np.empty((ids.size, self.n_vocab), np.float32) if want_logits else None
+        ms = C.c_float(0.0)
+        _check(_lib().hl_dense_batch_decode(self.handle, ids.ctypes.data_as(C.POINTER(_i32)), toks.ctypes.data_as(C.POINTER(_i32)),
+                                            ids.size, nxt.ctypes.data_as(C.POINTER(_i32)),
+                                            logits.ctypes.data_as(_f32p) if want_logits else None, C.byref(ms) if timed else None))
+        return (nxt, logits, ms.value) if timed else (nxt, logits)

@@ -129,6 +129,26 @@ int32_t hl_dense_forward_prefill_chunk(const int32_t* tokens_h, int32_t n, hl_kv
 int32_t hl_dense_forward_decode(int32_t token, hl_kv_cache* cache, float* logits_h);
 /* forwardDecodeTokenTimed: argmax on the device, optional device time of the step. */
 int32_t hl_dense_forward_decode_token_timed(int32_t token, hl_kv_cache* cache, int32_t* next_token, float* gpu_ms);
+/* ---- several sequences decoded together (continuous-batching hook) ------------------------------------------------
+ * No counterpart in the reference, which holds ONE sequence per process (inference.nim:28; the wish for batched
+ * serving is in docs/v3.5.md:24-35).  A batch owns one shared page pool for max_seqs sequences of up to max_len
+ * tokens; each decode step takes any subset of them, reads every weight once for all of their tokens, and runs the
+ * attention path over their separate block tables.  Needs a loaded model (hl_dense_load_model); destroy batches
+ * before unloading it. */
+typedef struct hl_dense_batch hl_dense_batch;
+int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_dense_batch** out);
+int32_t hl_dense_batch_destroy(hl_dense_batch* b);
+/* Tokens held by sequence `seq`, or -1. */
+int32_t hl_dense_batch_seq_len(const hl_dense_batch* b, int32_t seq);
+/* Prefill of one sequence: n tokens at positions start_pos .. (0 starts it over; up to its current length continues
+ * or re-uses a prefix); logits of the last of them [n_vocab]. */
+int32_t hl_dense_batch_prefill(hl_dense_batch* b, int32_t seq, const int32_t* tokens_h, int32_t n, int32_t start_pos,
+                               float* logits_h);
+/* One decode step: token tokens_h[i] is appended to sequence seq_ids_h[i] (distinct), i < n_active.  Outputs, either
+ * may be NULL: next_tokens_h[n_active] (argmax, first maximal index) and logits_h[n_active][n_vocab]. */
+int32_t hl_dense_batch_decode(hl_dense_batch* b, const int32_t* seq_ids_h, const int32_t* tokens_h, int32_t n_active,
+                              int32_t* next_tokens_h, float* logits_h, float* gpu_ms);
+
 /* Decode steps replay one captured CUDA graph per token (default on); 0 queues the kernels one by one instead.
  * Same results either way.  The reference's megakernel backend replays a HIP graph per token the same way
  * (src/hippo_leap/backends/megakernel.nim:2458-2479). */

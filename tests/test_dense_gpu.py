@@ -236,6 +236,71 @@ def test_dense_generate_loop_and_bench_cli(capsys):
     assert "Wall:" in out and "GPU :" in out
 
 
+@pytest.mark.parametrize("name", ["llama_hd64", "qwen3_hd128_qknorm"])
+def test_batched_decode_of_several_sequences(name):
+    """hl_dense_batch_*: five sequences of different lengths in one page pool; every step decodes a different subset
+    (5 rows: GEMV for up to 15 rows; 3 and 1: the fused decode projections; and a step after a prefix-reusing prefill).
+    Each row must equal what that sequence gives alone through forwardPrefill / forwardDecode, and the oracle."""
+    hp, qk_norm = CASES[name]
+    m = D.random_dense_model(hp, 41, qk_norm)
+    g = np.random.Generator(np.random.PCG64([41, 1]))
+    lens = [3, 40, 129, 17, 260]
+    prompts = [g.integers(0, hp.nVocab, n).astype(np.int32) for n in lens]
+    max_len = 280
+    D.loadModelBackend(m, hp)
+    batch = D.DecodeBatch(m, 6, max_len)
+    single = D.initKvCache(hp, max_len)
+    try:
+        refs, toks = [], []
+        for s, p in enumerate(prompts):
+            logits = batch.prefill(s, p)
+            single.curLen = 0
+            alone = D.forwardPrefill(m, p, single)
+            assert np.array_equal(logits, alone), "prefill in the shared pool differs from the private cache"
+            ref = OracleDense(m, max_len, True)
+            want = ref.forward(p)
+            assert_parity(logits, want, f"seq {s} prefill", max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
+            refs.append(ref)
+            toks.append(D.argmaxLast(want, hp.nVocab))
+            assert batch.seq_len(s) == len(p)
+        for step, active in enumerate([[0, 1, 2, 3, 4], [4, 2, 0], [1], [3, 0, 1, 2], [0, 1, 2, 3, 4]]):
+            nxt, logits = batch.decode(active, [toks[s] for s in active], want_logits=True)
+            for i, s in enumerate(active):
+                want = refs[s].forward([toks[s]])
+                scale = float(np.abs(want).max())
+                assert_parity(logits[i:i + 1], want, f"step {step} seq {s}", max_abs_tol=3e-3 * scale, rel_l2_tol=1.5e-3)
+                top2 = np.sort(want[0])[-2:]
+                toks[s] = D.argmaxLast(want, hp.nVocab)
+                assert nxt[i] == toks[s] or top2[1] - top2[0] <= 1e-2 * scale
+        assert [batch.seq_len(s) for s in range(5)] == [lens[0] + 4, lens[1] + 4, lens[2] + 4, lens[3] + 3, lens[4] + 3]
+        # the same step for one sequence alone, through the single-sequence contract on a private cache
+        single.curLen = 0
+        D.forwardPrefill(m, prompts[1], single)
+        b2 = D.DecodeBatch(m, 2, max_len)
+        b2.prefill(1, prompts[1])
+        t0 = 7
+        alone = D.forwardDecode(m, t0, single)
+        _, together = b2.decode([1], [t0], want_logits=True)
+        assert_parity(together, alone, "batch of one vs forwardDecode", max_abs_tol=1e-5 * float(np.abs(alone).max()) + 1e-6,
+                      rel_l2_tol=1e-5)
+        # prefix reuse inside the pool, then errors
+        b2.prefill(1, prompts[3], start_pos=20)
+        assert b2.seq_len(1) == 20 + lens[3]
+        with pytest.raises(ValueError, match="twice"):
+            b2.decode([1, 1], [1, 2])
+        with pytest.raises(ValueError, match="out of range"):
+            b2.decode([2], [1])
+        with pytest.raises(ValueError, match="start_pos"):
+            b2.prefill(0, prompts[0], start_pos=5)
+        with pytest.raises(ValueError, match="exceeds KV cache capacity"):
+            b2.prefill(0, np.zeros(max_len + 1, np.int32))
+        b2.close()
+    finally:
+        batch.close()
+        D.freeKvCache(single)
+        D.unloadModelBackend()
+
+
 def test_dense_contract_errors():
     hp, _ = CASES["llama_hd64"]
     m = D.random_dense_model(hp, 3)
