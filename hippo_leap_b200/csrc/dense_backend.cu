@@ -392,7 +392,8 @@ struct hl_dense_batch {
   int32_t* ctx_lens_d = nullptr;       // [max_seqs]
   int32_t *next_d = nullptr, *cand_i = nullptr;
   float *cand_v = nullptr, *logits_d = nullptr;  // [max_seqs][n_vocab]
-  int32_t* pinned = nullptr;           // [0..1] status, [2 ..] step inputs / next tokens
+  int32_t* pinned = nullptr;           // [0..1] status, then per step: next tokens [S], context lengths [S], token ids [S], tables [S][nb]
+  std::vector<cudaGraphExec_t> graphs; // one captured decode step per number of active sequences (index n)
 };
 
 extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_dense_batch** out) {
@@ -406,6 +407,7 @@ extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_d
   b->max_len = max_len;
   b->nb = (max_len + 127) / 128;
   b->cur_len.assign(max_seqs, 0);
+  b->graphs.assign(max_seqs + 1, nullptr);
   const size_t nt = static_cast<size_t>(max_seqs) * b->nb, V = d.hp.n_vocab;
   int32_t rc = hl_b200_kv_create(d.ctx, d.hp.n_layer, d.hp.n_head_kv, d.hp.head_dim, 128, static_cast<int32_t>(nt), &b->kv);
   std::vector<int32_t> ident(nt);
@@ -417,7 +419,7 @@ extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_d
                   cudaMalloc(&b->cand_i, static_cast<size_t>(max_seqs) * kArgmaxBlocks * 4) == cudaSuccess &&
                   cudaMalloc(&b->cand_v, static_cast<size_t>(max_seqs) * kArgmaxBlocks * 4) == cudaSuccess &&
                   cudaMalloc(&b->logits_d, static_cast<size_t>(max_seqs) * V * 4) == cudaSuccess &&
-                  cudaMallocHost(&b->pinned, (2 + 2 * static_cast<size_t>(max_seqs) + nt) * 4) == cudaSuccess;
+                  cudaMallocHost(&b->pinned, (2 + 3 * static_cast<size_t>(max_seqs) + nt) * 4) == cudaSuccess;
   if (!ok) {
     cudaGetLastError();
     hl_dense_batch_destroy(b);
@@ -438,6 +440,8 @@ extern "C" int32_t hl_dense_batch_destroy(hl_dense_batch* b) {
     if (*p) cudaFree(*p);
   for (float** p : {&b->cand_v, &b->logits_d})
     if (*p) cudaFree(*p);
+  for (cudaGraphExec_t ge : b->graphs)
+    if (ge) cudaGraphExecDestroy(ge);
   if (b->pinned) cudaFreeHost(b->pinned);
   delete b;
   return HL_OK;
@@ -468,41 +472,81 @@ extern "C" int32_t hl_dense_batch_decode(hl_dense_batch* b, const int32_t* seq_i
   if (!seq_ids_h || !tokens_h || (!next_tokens_h && !logits_h)) return dfail(HL_ERR_ARG, "null argument");
   if (n_active <= 0 || n_active > b->max_seqs) return dfail(HL_ERR_ARG, "n_active must be 1..max_seqs");
   D_CUDA(cudaSetDevice(d.device));
-  const int n = n_active, nb = b->nb;
-  int32_t* ctx_h = b->pinned + 2 + b->max_seqs;        // [n]
-  int32_t* tab_h = b->pinned + 2 + 2 * b->max_seqs;    // [n][nb]
-  std::vector<char> seen(b->max_seqs, 0);
+  const int n = n_active, nb = b->nb, S = b->max_seqs;
+  cudaStream_t st = d.ctx->stream;
+  D_CUDA(cudaStreamSynchronize(st));  // the pinned step record of the previous call has been consumed
+  int32_t* next_h = b->pinned + 2;        // [n]
+  int32_t* ctx_h = b->pinned + 2 + S;     // [n]
+  int32_t* tok_h = b->pinned + 2 + 2 * S; // [n]
+  int32_t* tab_h = b->pinned + 2 + 3 * S; // [n][nb]
+  std::vector<char> seen(S, 0);
   int max_ctx = 0;
   for (int i = 0; i < n; ++i) {
     const int s = seq_ids_h[i];
-    if (s < 0 || s >= b->max_seqs) return dfail(HL_ERR_ARG, "sequence index out of range");
+    if (s < 0 || s >= S) return dfail(HL_ERR_ARG, "sequence index out of range");
     if (seen[s]) return dfail(HL_ERR_ARG, "a sequence appears twice in one decode step");
     seen[s] = 1;
     if (b->cur_len[s] >= b->max_len) return dfail(HL_ERR_CAPACITY, "KV cache full");
     ctx_h[i] = b->cur_len[s] + 1;
+    tok_h[i] = tokens_h[i];
     max_ctx = ctx_h[i] > max_ctx ? ctx_h[i] : max_ctx;
     for (int j = 0; j < nb; ++j) tab_h[static_cast<size_t>(i) * nb + j] = s * nb + j;
   }
-  cudaStream_t st = d.ctx->stream;
-  D_CUDA(cudaStreamSynchronize(st));  // the pinned step record of the previous call has been consumed
-  if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
-  D_CUDA(cudaMemcpyAsync(b->ctx_lens_d, ctx_h, n * 4, cudaMemcpyHostToDevice, st));
-  D_CUDA(cudaMemcpyAsync(b->act_tables_d, tab_h, static_cast<size_t>(n) * nb * 4, cudaMemcpyHostToDevice, st));
-  BatchDecode bd{b->kv, b->ctx_lens_d, b->act_tables_d, nb, max_ctx, b->logits_d};
-  D_PASS(forward(tokens_h, n, 0, KvRef{}, true, 0, false, &bd));
-  if (next_tokens_h) {
+  // The step as a stream of work: inputs from the pinned record, every layer, argmax, results back to the record.
+  // `grid_ctx` sizes the attention grid: the real maximum for a plain launch, the capacity inside a graph.
+  auto enqueue = [&](int grid_ctx) -> int32_t {
+    D_CUDA(cudaMemcpyAsync(b->ctx_lens_d, ctx_h, n * 4, cudaMemcpyHostToDevice, st));
+    D_CUDA(cudaMemcpyAsync(b->act_tables_d, tab_h, static_cast<size_t>(n) * nb * 4, cudaMemcpyHostToDevice, st));
+    BatchDecode bd{b->kv, b->ctx_lens_d, b->act_tables_d, nb, grid_ctx, b->logits_d};
+    D_PASS(forward(tok_h, n, 0, KvRef{}, true, 0, false, &bd));
     argmax_partial<<<dim3(kArgmaxBlocks, n), 256, 0, st>>>(b->logits_d, d.hp.n_vocab, b->cand_v, b->cand_i);
     argmax_final<<<n, kArgmaxBlocks, 0, st>>>(b->cand_v, b->cand_i, b->next_d);
     d.ctx->launches += 2;
+    D_CUDA(cudaMemcpyAsync(next_h, b->next_d, n * 4, cudaMemcpyDeviceToHost, st));
+    D_CUDA(cudaMemcpyAsync(b->pinned, d.ctx->status_d, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    return HL_OK;
+  };
+  if (d.use_graph) {
+    if (!b->graphs[n]) {
+      // an uncaptured pass first (it sizes every scratch buffer; the replay repeats it with the same inputs)
+      D_PASS(enqueue(b->max_len));
+      D_CUDA(cudaStreamSynchronize(st));
+      const int64_t counted = d.ctx->launches;
+      D_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+      const int32_t rc = enqueue(b->max_len);
+      cudaGraph_t graph = nullptr;
+      const cudaError_t e = cudaStreamEndCapture(st, &graph);
+      d.ctx->launches = counted;  // recorded, not launched
+      if (rc != HL_OK || e != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc != HL_OK ? rc : dfail(HL_ERR_CUDA, "stream capture of the batched decode step failed");
+      }
+      const cudaError_t e2 = cudaGraphInstantiate(&b->graphs[n], graph, 0);
+      cudaGraphDestroy(graph);
+      if (e2 != cudaSuccess) {
+        b->graphs[n] = nullptr;
+        return dfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
+      }
+    }
+    if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
+    D_CUDA(cudaGraphLaunch(b->graphs[n], st));
+    if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, st));
+  } else {
+    if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
+    D_PASS(enqueue(max_ctx));
+    if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, st));
   }
-  if (gpu_ms) D_CUDA(cudaEventRecord(d.e1, st));
-  if (next_tokens_h) D_CUDA(cudaMemcpyAsync(b->pinned + 2, b->next_d, n * 4, cudaMemcpyDeviceToHost, st));
   if (logits_h)
     D_CUDA(cudaMemcpyAsync(logits_h, b->logits_d, static_cast<size_t>(n) * d.hp.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, st));
-  D_PASS(finish());
+  D_CUDA(cudaStreamSynchronize(st));
+  if (b->pinned[0] != 0) {
+    const int32_t code = b->pinned[0];
+    cudaMemset(d.ctx->status_d, 0, 2 * sizeof(int32_t));
+    return dfail(code, "a device-side check failed during the decode step");
+  }
   if (gpu_ms) D_CUDA(cudaEventElapsedTime(gpu_ms, d.e0, d.e1));
   for (int i = 0; i < n; ++i) {
-    if (next_tokens_h) next_tokens_h[i] = b->pinned[2 + i];
+    if (next_tokens_h) next_tokens_h[i] = next_h[i];
     b->cur_len[seq_ids_h[i]] += 1;
   }
   return HL_OK;

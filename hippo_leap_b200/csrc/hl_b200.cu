@@ -23,6 +23,7 @@
 #include "linear_f16.cuh"
 #include "linear_f16_pair.cuh"
 #include "linear_gemv.cuh"
+#include "linear_skinny.cuh"
 
 using namespace hl;
 
@@ -149,6 +150,8 @@ extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
   if (ctx->status_d) cudaFree(ctx->status_d);
   if (ctx->part_o) cudaFree(ctx->part_o);
   if (ctx->part_ml) cudaFree(ctx->part_ml);
+  if (ctx->skinny_part) cudaFree(ctx->skinny_part);
+  if (ctx->skinny_done) cudaFree(ctx->skinny_done);
   for (void* p : ctx->stage)
     if (p) cudaFree(p);
   if (ctx->cs_table) cudaFree(ctx->cs_table);
@@ -752,6 +755,57 @@ int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const 
   return launch_gemv_fused(ctx, p);
 }
 
+// 5 <= M <= 16: weight-streaming projection on warp MMAs (linear_skinny.cuh).  The kernel takes up to 64 rows, but
+// with more than 16 the activations staged per 64 rows of W weigh as much as W itself and the tcgen05 GEMM is faster.
+static int32_t launch_skinny(hl_ctx* ctx, const LinearArgs& g) {
+  const int m_pad = g.M <= 16 ? 16 : (g.M <= 32 ? 32 : 64);
+  const int kl_max = ((100 * 1024 / m_pad - 32) / 32) * 32;  // the A slice [m_pad][kl + 32] halfs stays below 200 KiB
+  const int blocks_n = (g.N + 63) / 64;
+  int splits = (g.K + kl_max - 1) / kl_max;
+  while (static_cast<int64_t>(blocks_n) * splits < 2 * ctx->n_sm && g.K / (splits * 2) >= 256) splits *= 2;
+  const int kl = (((g.K + splits - 1) / splits) + 31) / 32 * 32;
+  splits = (g.K + kl - 1) / kl;
+  SkinnyArgs p{};
+  p.g = g;
+  p.splits = splits;
+  p.kl = kl;
+  if (splits > 1) {
+    const size_t need = static_cast<size_t>(splits) * g.M * g.N;
+    if (need > ctx->skinny_cap || static_cast<size_t>(blocks_n) > ctx->skinny_done_cap) {  // grow-only scratch
+      HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      if (need > ctx->skinny_cap) {
+        if (ctx->skinny_part) cudaFree(ctx->skinny_part);
+        ctx->skinny_part = nullptr;
+        ctx->skinny_cap = 0;
+        HL_CUDA(ctx, cudaMalloc(&ctx->skinny_part, need * sizeof(float)));
+        ctx->skinny_cap = need;
+      }
+      if (static_cast<size_t>(blocks_n) > ctx->skinny_done_cap) {
+        if (ctx->skinny_done) cudaFree(ctx->skinny_done);
+        ctx->skinny_done = nullptr;
+        ctx->skinny_done_cap = 0;
+        HL_CUDA(ctx, cudaMalloc(&ctx->skinny_done, blocks_n * sizeof(int32_t)));
+        HL_CUDA(ctx, cudaMemset(ctx->skinny_done, 0, blocks_n * sizeof(int32_t)));
+        ctx->skinny_done_cap = blocks_n;
+      }
+    }
+    p.part = ctx->skinny_part;
+    p.done = ctx->skinny_done;
+  }
+  const size_t smem = static_cast<size_t>(m_pad) * (kl + ((kl & 63) == 0 ? 32 : 0)) * 2;
+  auto kern = m_pad == 16 ? linear_skinny_kernel<1> : (m_pad == 32 ? linear_skinny_kernel<2> : linear_skinny_kernel<4>);
+  static bool configured[16][3] = {};
+  bool& conf = configured[ctx->device & 15][m_pad == 16 ? 0 : (m_pad == 32 ? 1 : 2)];
+  if (!conf) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    conf = true;
+  }
+  kern<<<dim3(blocks_n, splits), 256, smem, ctx->stream>>>(p);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return HL_OK;
+}
+
 extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out,
                                       int32_t out_dtype, int64_t ldo, const float* resid, int64_t ldr, int32_t M,
                                       int32_t N, int32_t K, float* gpu_ms) {
@@ -783,6 +837,12 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
     p.g = g;
     p.mode = kGemvPlain;
     rc = launch_gemv_fused(ctx, p);
+    if (rc != HL_OK) return rc;
+    return hl_end_timing(ctx, gpu_ms);
+  }
+  static const bool no_skinny = getenv("HL_B200_NO_SKINNY") != nullptr;
+  if (M >= 5 && M <= 16 && !no_skinny && !(K & 7) && !(ldw & 7) && !(reinterpret_cast<uintptr_t>(w) & 15)) {
+    rc = launch_skinny(ctx, g);
     if (rc != HL_OK) return rc;
     return hl_end_timing(ctx, gpu_ms);
   }

@@ -236,8 +236,8 @@ def test_dense_generate_loop_and_bench_cli(capsys):
     assert "Wall:" in out and "GPU :" in out
 
 
-@pytest.mark.parametrize("name", ["llama_hd64", "qwen3_hd128_qknorm"])
-def test_batched_decode_of_several_sequences(name):
+@pytest.mark.parametrize("name,graph", [("llama_hd64", True), ("qwen3_hd128_qknorm", True), ("llama_hd64", False)])
+def test_batched_decode_of_several_sequences(name, graph):
     """hl_dense_batch_*: five sequences of different lengths in one page pool; every step decodes a different subset
     (5 rows: GEMV for up to 15 rows; 3 and 1: the fused decode projections; and a step after a prefix-reusing prefill).
     Each row must equal what that sequence gives alone through forwardPrefill / forwardDecode, and the oracle."""
@@ -247,6 +247,7 @@ def test_batched_decode_of_several_sequences(name):
     lens = [3, 40, 129, 17, 260]
     prompts = [g.integers(0, hp.nVocab, n).astype(np.int32) for n in lens]
     max_len = 280
+    D.setDecodeGraph(graph)   # a captured graph per number of active sequences, or plain launches
     D.loadModelBackend(m, hp)
     batch = D.DecodeBatch(m, 6, max_len)
     single = D.initKvCache(hp, max_len)
@@ -296,6 +297,7 @@ def test_batched_decode_of_several_sequences(name):
             b2.prefill(0, np.zeros(max_len + 1, np.int32))
         b2.close()
     finally:
+        D.setDecodeGraph(True)
         batch.close()
         D.freeKvCache(single)
         D.unloadModelBackend()
