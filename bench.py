@@ -276,31 +276,34 @@ def extra_linear(ctx, torch, device, peaks):
                                 "gate_up_16384x2048": (16384, 2048, 16), "down_2048x8192": (2048, 8192, 16),
                                 "vocab_128256x2048": (128256, 2048, 2)}.items():
             ws = (torch.randn((L, N, K), generator=gen, device=device) / K ** 0.5).half()
-            a = torch.randn((1, K), generator=gen, device=device).half()
-            out = torch.empty((1, N), dtype=torch.float32, device=device)
-            torch.cuda.synchronize()
-            with torch.cuda.stream(side):
-                for l in range(L):
-                    ctx2.linear_f16(a, ws[l], out)
-                side.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
+            for M in (1, 4, 16):
+                a = torch.randn((M, K), generator=gen, device=device).half()
+                out = torch.empty((M, N), dtype=torch.float32, device=device)
+                torch.cuda.synchronize()
+                with torch.cuda.stream(side):
                     for l in range(L):
                         ctx2.linear_f16(a, ws[l], out)
-                for _ in range(3):
-                    g.replay()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 20
-                e0.record(side)
-                for _ in range(reps):
-                    g.replay()
-                e1.record(side)
-                side.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (reps * L)
-            by = N * K * 2
-            res["gemv_" + name] = {"us_per_launch": us, "weight_gbs": by / (us * 1e-6) / 1e9,
-                                   "frac_of_hbm_peak": by / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
-            del ws, a, out, g
+                    side.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        for l in range(L):
+                            ctx2.linear_f16(a, ws[l], out)
+                    for _ in range(3):
+                        g.replay()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 20
+                    e0.record(side)
+                    for _ in range(reps):
+                        g.replay()
+                    e1.record(side)
+                    side.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+                by = N * K * 2
+                res[f"gemv_{name}" + ("" if M == 1 else f"_x{M}rows")] = {
+                    "us_per_launch": us, "weight_gbs": by / (us * 1e-6) / 1e9,
+                    "frac_of_hbm_peak": by / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+                del a, out, g
+            del ws
             torch.cuda.empty_cache()
     finally:
         ctx2.close()

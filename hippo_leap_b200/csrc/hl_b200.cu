@@ -793,9 +793,12 @@ static int32_t launch_skinny(hl_ctx* ctx, const LinearArgs& g) {
     p.done = ctx->skinny_done;
   }
   const size_t smem = static_cast<size_t>(m_pad) * (kl + ((kl & 63) == 0 ? 32 : 0)) * 2;
-  auto kern = m_pad == 16 ? linear_skinny_kernel<1> : (m_pad == 32 ? linear_skinny_kernel<2> : linear_skinny_kernel<4>);
-  static bool configured[16][3] = {};
-  bool& conf = configured[ctx->device & 15][m_pad == 16 ? 0 : (m_pad == 32 ? 1 : 2)];
+  const bool deep = kl <= 256;  // one round of loads covers the split
+  auto kern = m_pad == 16 ? (deep ? linear_skinny_kernel<1, 8> : linear_skinny_kernel<1, 4>)
+                          : (m_pad == 32 ? (deep ? linear_skinny_kernel<2, 8> : linear_skinny_kernel<2, 4>)
+                                         : (deep ? linear_skinny_kernel<4, 8> : linear_skinny_kernel<4, 4>));
+  static bool configured[16][6] = {};
+  bool& conf = configured[ctx->device & 15][(m_pad == 16 ? 0 : (m_pad == 32 ? 1 : 2)) * 2 + (deep ? 1 : 0)];
   if (!conf) {
     HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     conf = true;

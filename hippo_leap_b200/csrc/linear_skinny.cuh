@@ -4,7 +4,7 @@
 // them), so they go to the tensor cores through warp MMAs, with the token rows padded to 16 / 32 / 64.
 //
 //   block = 64 rows of W (one 8-row group per warp) x one split of K;  grid = (ceil(N / 64), splits)
-//   * every lane's 16-byte loads of W (eight 32-wide K steps in flight, issued before anything else) ARE the B
+//   * every lane's 16-byte loads of W (four or eight 32-wide K steps in flight, issued before anything else) ARE the B
 //     fragments of two m16n8k16 MMAs: lane (g, t) holds W[n0 + g][k + 8t .. 8t + 7]; the first four halfs serve
 //     MMA 0 (logical k 2t, 2t+1, 2t+8, 2t+9), the last four MMA 1.  The A fragments read the activations with the
 //     same permutation of k, so each physical k is multiplied exactly once -- no shuffles, no shared-memory staging
@@ -30,7 +30,9 @@ struct SkinnyArgs {
   int32_t splits, kl;  // kl: K per split, multiple of 32
 };
 
-template <int MT>  // 16-row tiles of token rows: M <= 16 * MT
+// MT: 16-row tiles of token rows (M <= 16 * MT).  kDepth: 32-wide K steps of W in flight per lane -- 8 covers a whole
+// 256-wide split with one round of loads; 4 keeps the register count low enough for five blocks per SM on long splits.
+template <int MT, int kDepth>
 __global__ void __launch_bounds__(256) linear_skinny_kernel(SkinnyArgs p) {
   extern __shared__ __align__(16) uint8_t skinny_smem[];
   const LinearArgs& g = p.g;
@@ -43,7 +45,6 @@ __global__ void __launch_bounds__(256) linear_skinny_kernel(SkinnyArgs p) {
   const int lda_s = p.kl + ((p.kl & 63) == 0 ? 32 : 0);
   __half* a_s = reinterpret_cast<__half*>(skinny_smem);
 
-  constexpr int kDepth = 8;
   uint4 wreg[kDepth];
   const int k_lane = kb + 8 * t;
 #pragma unroll
