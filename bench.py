@@ -276,7 +276,7 @@ def extra_linear(ctx, torch, device, peaks):
                                 "gate_up_16384x2048": (16384, 2048, 16), "down_2048x8192": (2048, 8192, 16),
                                 "vocab_128256x2048": (128256, 2048, 2)}.items():
             ws = (torch.randn((L, N, K), generator=gen, device=device) / K ** 0.5).half()
-            for M in (1, 4, 16):
+            for M in (1, 4, 16, 64):
                 a = torch.randn((M, K), generator=gen, device=device).half()
                 out = torch.empty((M, N), dtype=torch.float32, device=device)
                 torch.cuda.synchronize()

@@ -217,7 +217,9 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, KvRef ref, bool decode
     if (decode && !bd) set_i32<<<1, 1, 0, st>>>(d.ctx_len_d, pos0 + 1);
   }
   if (grid_ctx < pos0 + 1) grid_ctx = pos0 + 1;
-  const bool fused = n <= 4;  // decode-sized: RMSNorm and SwiGLU run as prologues of the projection that follows them
+  // one row: RMSNorm and SwiGLU run as prologue / epilogue of the GEMV next to them; more rows go through the row
+  // kernels and the tcgen05 projections
+  const bool fused = n == 1;
   embedding_f16_kernel<<<n, 128, 0, st>>>(d.tok_emb, d.tokens_d, E, hp.n_vocab, d.x);
   d.ctx->launches += 2;
   for (int l = 0; l < hp.n_layer; ++l) {

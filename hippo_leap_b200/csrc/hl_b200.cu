@@ -23,7 +23,7 @@
 #include "linear_f16.cuh"
 #include "linear_f16_pair.cuh"
 #include "linear_gemv.cuh"
-#include "linear_skinny.cuh"
+#include "linear_wide.cuh"
 
 using namespace hl;
 
@@ -150,8 +150,7 @@ extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
   if (ctx->status_d) cudaFree(ctx->status_d);
   if (ctx->part_o) cudaFree(ctx->part_o);
   if (ctx->part_ml) cudaFree(ctx->part_ml);
-  if (ctx->skinny_part) cudaFree(ctx->skinny_part);
-  if (ctx->skinny_done) cudaFree(ctx->skinny_done);
+  if (ctx->splitk_part) cudaFree(ctx->splitk_part);
   for (void* p : ctx->stage)
     if (p) cudaFree(p);
   if (ctx->cs_table) cudaFree(ctx->cs_table);
@@ -755,58 +754,59 @@ int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const 
   return launch_gemv_fused(ctx, p);
 }
 
-// 5 <= M <= 16: weight-streaming projection on warp MMAs (linear_skinny.cuh).  The kernel takes up to 64 rows, but
-// with more than 16 the activations staged per 64 rows of W weigh as much as W itself and the tcgen05 GEMM is faster.
-static int32_t launch_skinny(hl_ctx* ctx, const LinearArgs& g) {
-  const int m_pad = g.M <= 16 ? 16 : (g.M <= 32 ? 32 : 64);
-  const int kl_max = ((100 * 1024 / m_pad - 32) / 32) * 32;  // the A slice [m_pad][kl + 32] halfs stays below 200 KiB
-  const int blocks_n = (g.N + 63) / 64;
-  int splits = (g.K + kl_max - 1) / kl_max;
-  while (static_cast<int64_t>(blocks_n) * splits < 2 * ctx->n_sm && g.K / (splits * 2) >= 256) splits *= 2;
-  const int kl = (((g.K + splits - 1) / splits) + 31) / 32 * 32;
-  splits = (g.K + kl - 1) / kl;
-  SkinnyArgs p{};
-  p.g = g;
-  p.splits = splits;
-  p.kl = kl;
-  if (splits > 1) {
-    const size_t need = static_cast<size_t>(splits) * g.M * g.N;
-    if (need > ctx->skinny_cap || static_cast<size_t>(blocks_n) > ctx->skinny_done_cap) {  // grow-only scratch
-      HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-      if (need > ctx->skinny_cap) {
-        if (ctx->skinny_part) cudaFree(ctx->skinny_part);
-        ctx->skinny_part = nullptr;
-        ctx->skinny_cap = 0;
-        HL_CUDA(ctx, cudaMalloc(&ctx->skinny_part, need * sizeof(float)));
-        ctx->skinny_cap = need;
-      }
-      if (static_cast<size_t>(blocks_n) > ctx->skinny_done_cap) {
-        if (ctx->skinny_done) cudaFree(ctx->skinny_done);
-        ctx->skinny_done = nullptr;
-        ctx->skinny_done_cap = 0;
-        HL_CUDA(ctx, cudaMalloc(&ctx->skinny_done, blocks_n * sizeof(int32_t)));
-        HL_CUDA(ctx, cudaMemset(ctx->skinny_done, 0, blocks_n * sizeof(int32_t)));
-        ctx->skinny_done_cap = blocks_n;
-      }
-    }
-    p.part = ctx->skinny_part;
-    p.done = ctx->skinny_done;
-  }
-  const size_t smem = static_cast<size_t>(m_pad) * (kl + ((kl & 63) == 0 ? 32 : 0)) * 2;
-  const bool deep = kl <= 256;  // one round of loads covers the split
-  auto kern = m_pad == 16 ? (deep ? linear_skinny_kernel<1, 8> : linear_skinny_kernel<1, 4>)
-                          : (m_pad == 32 ? (deep ? linear_skinny_kernel<2, 8> : linear_skinny_kernel<2, 4>)
-                                         : (deep ? linear_skinny_kernel<4, 8> : linear_skinny_kernel<4, 4>));
-  static bool configured[16][6] = {};
-  bool& conf = configured[ctx->device & 15][(m_pad == 16 ? 0 : (m_pad == 32 ? 1 : 2)) * 2 + (deep ? 1 : 0)];
-  if (!conf) {
-    HL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    conf = true;
-  }
-  kern<<<dim3(blocks_n, splits), 256, smem, ctx->stream>>>(p);
+// split-K scratch of the several-row projection (grow-only), and the launch of the reduction behind it
+static int32_t ensure_splitk(hl_ctx* ctx, size_t floats) {
+  if (floats <= ctx->splitk_cap) return HL_OK;
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->splitk_part) cudaFree(ctx->splitk_part);
+  ctx->splitk_part = nullptr;
+  ctx->splitk_cap = 0;
+  HL_CUDA(ctx, cudaMalloc(&ctx->splitk_part, floats * sizeof(float)));
+  ctx->splitk_cap = floats;
+  return HL_OK;
+}
+static int32_t launch_splitk_reduce(hl_ctx* ctx, const LinearArgs& g, int splits) {
+  const int64_t quads = static_cast<int64_t>((g.N + 3) / 4) * g.M;
+  splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, ctx->stream>>>(ctx->splitk_part, splits, g);
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;
+}
+
+static int32_t make_map_2d(hl_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                           int box_rows);
+
+// 2 <= M <= 128: tcgen05 with W on the M side of the MMA (linear_wide.cuh)
+static int32_t launch_wide(hl_ctx* ctx, const LinearArgs& g) {
+  using Cfg = LinearWideCfg;
+  const int tiles_n = (g.N + Cfg::BW - 1) / Cfg::BW;
+  int splits = 1;
+  while (static_cast<int64_t>(tiles_n) * splits < 2 * ctx->n_sm && g.K / (splits * 2) >= 256) splits *= 2;  // two CTAs per SM
+  const int kl = (((g.K + splits - 1) / splits) + 63) / 64 * 64;
+  splits = (g.K + kl - 1) / kl;
+  WideArgs p{};
+  p.g = g;
+  p.splits = splits;
+  p.kl = kl;
+  p.m_pad = (g.M + 15) / 16 * 16;
+  if (splits > 1) {
+    const int32_t rc = ensure_splitk(ctx, static_cast<size_t>(splits) * g.M * g.N);
+    if (rc != HL_OK) return rc;
+    p.part = ctx->splitk_part;
+  }
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    HL_CUDA(ctx, cudaFuncSetAttribute(linear_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[ctx->device & 15] = true;
+  }
+  CUtensorMap w_map, a_map;
+  int32_t rc = make_map_2d(ctx, &w_map, g.w, g.N, g.K, g.ldw, Cfg::BW);
+  if (rc == HL_OK) rc = make_map_2d(ctx, &a_map, g.a, g.M, g.K, g.lda, p.m_pad);
+  if (rc != HL_OK) return rc;
+  linear_wide_kernel<<<dim3(tiles_n, splits), Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(w_map, a_map, p);
+  ctx->launches++;
+  HL_CUDA(ctx, cudaGetLastError());
+  return splits > 1 ? launch_splitk_reduce(ctx, g, splits) : HL_OK;
 }
 
 extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out,
@@ -834,18 +834,19 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
   g.status = ctx->status_d;
   int32_t rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
+  static const bool no_wide = getenv("HL_B200_NO_WIDE") != nullptr;
+  if (M >= 2 && M <= 128 && !no_wide && !(lda & 7) && !(ldw & 7) && !(reinterpret_cast<uintptr_t>(a) & 15) &&
+      !(reinterpret_cast<uintptr_t>(w) & 15)) {
+    rc = launch_wide(ctx, g);
+    if (rc != HL_OK) return rc;
+    return hl_end_timing(ctx, gpu_ms);
+  }
   if (M <= 4 && !(K & 7) && !(ldw & 7) && ldw < (1 << 28) && !(reinterpret_cast<uintptr_t>(w) & 15) &&
       static_cast<size_t>(M) * K * 2 + 512 <= 200 * 1024) {
     GemvArgs p{};
     p.g = g;
     p.mode = kGemvPlain;
     rc = launch_gemv_fused(ctx, p);
-    if (rc != HL_OK) return rc;
-    return hl_end_timing(ctx, gpu_ms);
-  }
-  static const bool no_skinny = getenv("HL_B200_NO_SKINNY") != nullptr;
-  if (M >= 5 && M <= 16 && !no_skinny && !(K & 7) && !(ldw & 7) && !(reinterpret_cast<uintptr_t>(w) & 15)) {
-    rc = launch_skinny(ctx, g);
     if (rc != HL_OK) return rc;
     return hl_end_timing(ctx, gpu_ms);
   }

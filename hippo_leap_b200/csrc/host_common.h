@@ -22,10 +22,8 @@ struct hl_ctx {
   float* part_o = nullptr;      // split-KV partial outputs (grow-only scratch)
   float* part_ml = nullptr;     // split-KV partial (max, sum)
   size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
-  float* skinny_part = nullptr;   // split-K partial tiles of the several-row decode projection
-  size_t skinny_cap = 0;          // in floats
-  int32_t* skinny_done = nullptr; // its arrival counters per 64-row group of W; zero between launches
-  size_t skinny_done_cap = 0;
+  float* splitk_part = nullptr;   // split-K partial tiles of the several-row projections
+  size_t splitk_cap = 0;          // in floats
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // q, k, v, out staging of the *_host calls
   size_t stage_cap[4] = {0, 0, 0, 0};
   void* cs_table = nullptr;  // float2 [cs_len][cs_half]: (cos, sin) of float(pos) * theta_i

@@ -40,18 +40,19 @@ def test_gemv_against_oracle_matmul(hl_ctx, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K,resid,dt", [
-    (5, 64, 32, False, torch.float32),          # one block, one K step, M padded to 16
+    (2, 64, 32, False, torch.float32),          # two rows padded to 16, one K step
+    (5, 64, 32, False, torch.float32),
     (9, 3072, 2048, False, torch.float32),      # Q|K|V shape, eight splits
-    (12, 128, 8200, True, torch.float16),       # K not a multiple of 32: lanes past the end multiply zeros
-    (16, 2048, 2048, True, torch.float32),      # split-K with the last-arriving block adding the partials
-    (17, 300, 200, True, torch.float16),        # 32-row padding, ragged N (row clamp) and K (zero tail)
+    (12, 128, 8200, True, torch.float16),       # K not a multiple of 64: the TMA box past the end is zero
+    (16, 2048, 2048, True, torch.float32),      # split-K, partials added by the reduction kernel
+    (17, 300, 200, True, torch.float16),        # 32-row padding, ragged N and K
     (33, 1000, 4096, False, torch.float32),     # 64-row padding
     (64, 2048, 8192, True, torch.float32),      # the down projection of a 64-sequence step
     (40, 16384, 2048, False, torch.float16),    # gate|up shape: no split
 ])
-def test_several_row_decode_projection_against_oracle_matmul(hl_ctx, M, N, K, resid, dt):
-    """5 <= M <= 16 runs on warp MMAs with W streamed once (linear_skinny.cuh), more rows on the tcgen05 GEMM; twice
-    in a row, so that the arrival counters of the split-K form are seen to re-arm."""
+def test_several_row_projection_against_oracle_matmul(hl_ctx, M, N, K, resid, dt):
+    """2 <= M <= 128 runs on tcgen05 with W on the M side of the MMA and split-K for short N (linear_wide.cuh); twice
+    in a row on different data, so that stale split-K partials would show."""
     _check(hl_ctx, M, N, K, resid=resid, out_dtype=dt, seed=M + N)
     _check(hl_ctx, M, N, K, resid=resid, out_dtype=dt, seed=M + N + 1)
 
