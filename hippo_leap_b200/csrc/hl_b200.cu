@@ -781,7 +781,8 @@ static int32_t launch_wide(hl_ctx* ctx, const LinearArgs& g) {
   using Cfg = LinearWideCfg;
   const int tiles_n = (g.N + Cfg::BW - 1) / Cfg::BW;
   int splits = 1;
-  while (static_cast<int64_t>(tiles_n) * splits < 2 * ctx->n_sm && g.K / (splits * 2) >= 256) splits *= 2;  // two CTAs per SM
+  // as many splits as still fit one wave of two CTAs per SM (a second, partly filled wave costs more than it buys)
+  while (static_cast<int64_t>(tiles_n) * splits * 2 <= 2 * ctx->n_sm && g.K / (splits * 2) >= 256) splits *= 2;
   const int kl = (((g.K + splits - 1) / splits) + 63) / 64 * 64;
   splits = (g.K + kl - 1) / kl;
   WideArgs p{};
