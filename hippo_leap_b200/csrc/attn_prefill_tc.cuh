@@ -775,6 +775,7 @@ static int32_t hl_prefill_tc_fill_args(hl_ctx* ctx, hl_kv* kv, const hl::Prefill
       if (ctx->cs_table) cudaFree(ctx->cs_table);
       ctx->cs_table = nullptr;
       ctx->cs_len = 0;
+      ctx->scratch_epoch++;
       const int cap = ((n_pos + 4095) / 4096) * 4096;
       HL_CUDA(ctx, cudaMalloc(&ctx->cs_table, static_cast<size_t>(cap) * half * sizeof(float2)));
       const int64_t total = static_cast<int64_t>(cap) * half;

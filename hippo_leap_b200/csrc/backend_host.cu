@@ -13,6 +13,7 @@ int32_t ensure_stage(hl_ctx* ctx, int i, size_t bytes) {
   if (ctx->stage[i]) cudaFree(ctx->stage[i]);
   ctx->stage[i] = nullptr;
   ctx->stage_cap[i] = 0;
+  ctx->scratch_epoch++;
   HL_CUDA(ctx, cudaMalloc(&ctx->stage[i], bytes));
   ctx->stage_cap[i] = bytes;
   return HL_OK;

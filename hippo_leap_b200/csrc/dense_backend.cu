@@ -40,6 +40,8 @@ struct Dense {
   cudaGraphExec_t graph = nullptr;
   void* graph_kv = nullptr;
   int graph_max_len = 0;
+  uint64_t buf_epoch = 0;                        // bumped when the activation buffers are re-allocated
+  uint64_t graph_buf_epoch = 0, graph_ctx_epoch = 0;  // what the captured graph was recorded against
   int64_t graph_kernels = 0;  // kernels inside one replay
   std::string err;
 } d;
@@ -106,6 +108,7 @@ int32_t ensure_act(int n) {
   if (d.tokens_d) cudaFree(d.tokens_d);
   d.tokens_d = nullptr;
   d.cap = 0;
+  d.buf_epoch++;
   const size_t E = d.hp.n_emb, F = d.hp.n_ffn, qd = static_cast<size_t>(d.hp.n_head) * d.hp.head_dim,
                kd = static_cast<size_t>(d.hp.n_head_kv) * d.hp.head_dim, N = n;
   D_CUDA(cudaMalloc(&d.x, N * E * sizeof(float)));
@@ -323,7 +326,10 @@ int32_t check_cache(const hl_kv_cache* cache) {
 // Capture one decode step (every layer, logits, argmax, result and status copies) into a CUDA graph.  The decode grid
 // and the split-KV scratch are sized for the cache's capacity, so one graph serves every position.
 int32_t ensure_decode_graph(hl_kv_cache* cache) {
-  if (d.graph && d.graph_kv == cache->gpu_cache && d.graph_max_len == cache->max_len) return HL_OK;
+  // still valid: same cache, and no buffer whose address the graph holds has been re-allocated since
+  if (d.graph && d.graph_kv == cache->gpu_cache && d.graph_max_len == cache->max_len && d.graph_buf_epoch == d.buf_epoch &&
+      d.graph_ctx_epoch == d.ctx->scratch_epoch)
+    return HL_OK;
   if (d.graph) cudaGraphExecDestroy(d.graph);
   d.graph = nullptr;
   cudaStream_t st = d.ctx->stream;
@@ -353,6 +359,8 @@ int32_t ensure_decode_graph(hl_kv_cache* cache) {
   if (e != cudaSuccess) return dfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
   d.graph_kv = cache->gpu_cache;
   d.graph_max_len = cache->max_len;
+  d.graph_buf_epoch = d.buf_epoch;
+  d.graph_ctx_epoch = d.ctx->scratch_epoch;
   return HL_OK;
 }
 
@@ -396,6 +404,7 @@ struct hl_dense_batch {
   float *cand_v = nullptr, *logits_d = nullptr;  // [max_seqs][n_vocab]
   int32_t* pinned = nullptr;           // [0..1] status, then per step: next tokens [S], context lengths [S], token ids [S], tables [S][nb]
   std::vector<cudaGraphExec_t> graphs; // one captured decode step per number of active sequences (index n)
+  std::vector<uint64_t> graph_epoch;   // buffer epochs (activations + library scratch) each was recorded against
 };
 
 extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_dense_batch** out) {
@@ -410,6 +419,7 @@ extern "C" int32_t hl_dense_batch_create(int32_t max_seqs, int32_t max_len, hl_d
   b->nb = (max_len + 127) / 128;
   b->cur_len.assign(max_seqs, 0);
   b->graphs.assign(max_seqs + 1, nullptr);
+  b->graph_epoch.assign(max_seqs + 1, 0);
   const size_t nt = static_cast<size_t>(max_seqs) * b->nb, V = d.hp.n_vocab;
   int32_t rc = hl_b200_kv_create(d.ctx, d.hp.n_layer, d.hp.n_head_kv, d.hp.head_dim, 128, static_cast<int32_t>(nt), &b->kv);
   std::vector<int32_t> ident(nt);
@@ -509,6 +519,10 @@ extern "C" int32_t hl_dense_batch_decode(hl_dense_batch* b, const int32_t* seq_i
     return HL_OK;
   };
   if (d.use_graph) {
+    if (b->graphs[n] && b->graph_epoch[n] != d.buf_epoch + d.ctx->scratch_epoch) {  // a buffer it points to has moved
+      cudaGraphExecDestroy(b->graphs[n]);
+      b->graphs[n] = nullptr;
+    }
     if (!b->graphs[n]) {
       // an uncaptured pass first (it sizes every scratch buffer; the replay repeats it with the same inputs)
       D_PASS(enqueue(b->max_len));
@@ -529,6 +543,7 @@ extern "C" int32_t hl_dense_batch_decode(hl_dense_batch* b, const int32_t* seq_i
         b->graphs[n] = nullptr;
         return dfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
       }
+      b->graph_epoch[n] = d.buf_epoch + d.ctx->scratch_epoch;  // both only ever grow, so the sum changes when either does
     }
     if (gpu_ms) D_CUDA(cudaEventRecord(d.e0, st));
     D_CUDA(cudaGraphLaunch(b->graphs[n], st));

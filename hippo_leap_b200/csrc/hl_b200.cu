@@ -279,6 +279,7 @@ extern "C" int32_t hl_b200_set_rope(hl_ctx* ctx, const float* theta_h, int32_t h
   if (ctx->theta_half < half) {
     if (ctx->theta_d) cudaFree(ctx->theta_d);
     ctx->theta_d = nullptr;
+    ctx->scratch_epoch++;
     HL_CUDA(ctx, cudaMalloc(&ctx->theta_d, half * sizeof(float)));
   }
   ctx->theta_half = half;
@@ -501,6 +502,7 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
       if (ctx->part_ml) cudaFree(ctx->part_ml);
       ctx->part_o = ctx->part_ml = nullptr;
       ctx->part_cap = 0;
+      ctx->scratch_epoch++;
       HL_CUDA(ctx, cudaMalloc(&ctx->part_o, need * 128 * sizeof(float)));
       HL_CUDA(ctx, cudaMalloc(&ctx->part_ml, need * 2 * sizeof(float)));
       ctx->part_cap = need;
@@ -761,6 +763,7 @@ static int32_t ensure_splitk(hl_ctx* ctx, size_t floats) {
   if (ctx->splitk_part) cudaFree(ctx->splitk_part);
   ctx->splitk_part = nullptr;
   ctx->splitk_cap = 0;
+  ctx->scratch_epoch++;
   HL_CUDA(ctx, cudaMalloc(&ctx->splitk_part, floats * sizeof(float)));
   ctx->splitk_cap = floats;
   return HL_OK;

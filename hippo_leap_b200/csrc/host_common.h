@@ -22,6 +22,9 @@ struct hl_ctx {
   float* part_o = nullptr;      // split-KV partial outputs (grow-only scratch)
   float* part_ml = nullptr;     // split-KV partial (max, sum)
   size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
+  // Bumped whenever one of the grow-only scratch buffers below is re-allocated: a captured CUDA graph that baked
+  // the old address in must be captured again (the backends compare this before every replay).
+  uint64_t scratch_epoch = 0;
   float* splitk_part = nullptr;   // split-K partial tiles of the several-row projections
   size_t splitk_cap = 0;          // in floats
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // q, k, v, out staging of the *_host calls

@@ -35,6 +35,8 @@ struct Backend {
   cudaGraphExec_t graph = nullptr;  // one decode step (all layers) captured once per (cache, max_len)
   const void* graph_kv = nullptr;
   int graph_max_len = 0;
+  uint64_t buf_epoch = 0;                             // bumped when an activation / token buffer is re-allocated
+  uint64_t graph_buf_epoch = 0, graph_ctx_epoch = 0;  // what the captured graph was recorded against
   bool use_graph = true;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   std::string err;
@@ -158,6 +160,7 @@ int32_t ensure_act(int n_tok) {
     *p = nullptr;
   }
   g.act_cap = 0;
+  g.buf_epoch++;
   const size_t qd = static_cast<size_t>(g.hp.n_head) * g.hp.head_dim, kd = static_cast<size_t>(g.hp.n_head_kv) * g.hp.head_dim;
   B_CUDA(cudaMalloc(&g.q, n_tok * qd * sizeof(float)));
   B_CUDA(cudaMalloc(&g.k, n_tok * kd * sizeof(float)));
@@ -195,6 +198,7 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     cudaStreamSynchronize(g.ctx->stream);
     if (g.tokens_d) cudaFree(g.tokens_d);
     g.tokens_d = nullptr;
+    g.buf_epoch++;
     B_CUDA(cudaMalloc(&g.tokens_d, n * sizeof(int32_t)));
     g.tokens_cap = n;
   }
@@ -406,7 +410,10 @@ extern "C" int32_t hl_backend_forward_decode(int32_t token, hl_kv_cache* cache, 
 // The grid and the split-KV scratch are sized for the cache's full capacity, so the same graph serves
 // every position: CTAs of chunks beyond the current context exit at once.
 static int32_t ensure_decode_graph(hl_kv_cache* cache) {
-  if (g.graph && g.graph_kv == cache->gpu_cache && g.graph_max_len == cache->max_len) return HL_OK;
+  // still valid: same cache, and no buffer whose address the graph holds has been re-allocated since
+  if (g.graph && g.graph_kv == cache->gpu_cache && g.graph_max_len == cache->max_len && g.graph_buf_epoch == g.buf_epoch &&
+      g.graph_ctx_epoch == g.ctx->scratch_epoch)
+    return HL_OK;
   if (g.graph) cudaGraphExecDestroy(g.graph);
   g.graph = nullptr;
   cudaStream_t st = g.ctx->stream;
@@ -435,6 +442,8 @@ static int32_t ensure_decode_graph(hl_kv_cache* cache) {
   if (e != cudaSuccess) return bfail(HL_ERR_CUDA, "cudaGraphInstantiate failed");
   g.graph_kv = cache->gpu_cache;
   g.graph_max_len = cache->max_len;
+  g.graph_buf_epoch = g.buf_epoch;
+  g.graph_ctx_epoch = g.ctx->scratch_epoch;
   return HL_OK;
 }
 
