@@ -227,3 +227,34 @@ def test_chunked_prefill_and_prefix_reuse_stand_in_model():
     finally:
         B.freeKvCache(cache)
         B.unloadModelBackend()
+
+
+def test_decode_graph_is_recaptured_when_a_longer_prompt_grows_the_buffers():
+    """The captured decode step holds the addresses of the grow-only activation buffers; a longer prompt re-allocates
+    them, and the next replay must use the new ones."""
+    hp = B.HParams(nVocab=512, nLayer=2, nHead=8, nHeadKv=2, headDim=64)
+    m = B.standin_model(hp, 17)
+    max_len = 400
+    cache = B.initKvCache(hp, max_len)
+    B.loadModelBackend(m, hp)
+    B.setDecodeGraph(True)
+    try:
+        ref = OracleModel(m, max_len, hp.ropeMode)
+        g = np.random.Generator(np.random.PCG64([17, 1]))
+        for n in (3, 350, 6):
+            prompt = g.integers(0, hp.nVocab, n).astype(np.int32)
+            cache.curLen = 0
+            ref.reset()
+            want = ref.forward(prompt)
+            assert_parity(B.forwardPrefill(m, prompt, cache), want, "prefill", max_abs_tol=2e-3 * float(np.abs(want).max()),
+                          rel_l2_tol=1e-3)
+            tok = B.argmaxLast(want, hp.nVocab)
+            for _ in range(4):
+                got = B.forwardDecodeToken(m, tok, cache)
+                want = ref.forward([tok])
+                top2 = np.sort(want[0])[-2:]
+                tok = B.argmaxLast(want, hp.nVocab)
+                assert got == tok or top2[1] - top2[0] < 1e-3 * float(np.abs(want).max())
+    finally:
+        B.freeKvCache(cache)
+        B.unloadModelBackend()

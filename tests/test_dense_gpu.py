@@ -303,6 +303,52 @@ def test_batched_decode_of_several_sequences(name, graph):
         D.unloadModelBackend()
 
 
+def test_decode_graphs_are_recaptured_when_buffers_grow():
+    """A captured decode step holds the addresses of grow-only buffers.  A longer prompt (activations), a larger batch
+    (split-KV and split-K scratch) re-allocate them; the next replay must run on the new ones."""
+    hp, qk_norm = CASES["llama_hd64"]
+    m = D.random_dense_model(hp, 51, qk_norm)
+    g = np.random.Generator(np.random.PCG64([51, 1]))
+    short, long_ = g.integers(0, hp.nVocab, 4).astype(np.int32), g.integers(0, hp.nVocab, 300).astype(np.int32)
+    max_len = 320
+    D.setDecodeGraph(True)
+    cache = D.initKvCache(hp, max_len)
+    D.loadModelBackend(m, hp)
+    try:
+        ref = OracleDense(m, max_len, True)
+        for prompt in (short, long_, short):          # the long prompt re-allocates the activations between graph replays
+            cache.curLen = 0
+            for c in ref.caches:
+                c.cur_len = 0
+            want = ref.forward(prompt)
+            assert_parity(D.forwardPrefill(m, prompt, cache), want, "prefill", max_abs_tol=3e-3 * float(np.abs(want).max()),
+                          rel_l2_tol=1.5e-3)
+            tok = D.argmaxLast(want, hp.nVocab)
+            for _ in range(3):
+                got, want = D.forwardDecode(m, tok, cache), ref.forward([tok])
+                assert_parity(got, want, "decode", max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
+                tok = D.argmaxLast(want, hp.nVocab)
+        batch = D.DecodeBatch(m, 8, max_len)
+        try:
+            refs = [OracleDense(m, max_len, True) for _ in range(8)]
+            toks = []
+            for s_ in range(8):
+                p_ = g.integers(0, hp.nVocab, 10 + 30 * s_).astype(np.int32)
+                batch.prefill(s_, p_)
+                toks.append(D.argmaxLast(refs[s_].forward(p_), hp.nVocab))
+            for active in ([0], [1, 2], [0, 1, 2, 3, 4, 5, 6, 7], [0], [3, 1], [7, 6, 5, 4, 3, 2, 1, 0]):  # small graphs first
+                _, logits = batch.decode(active, [toks[s_] for s_ in active], want_logits=True)
+                for i, s_ in enumerate(active):
+                    want = refs[s_].forward([toks[s_]])
+                    assert_parity(logits[i:i + 1], want, f"batch {active} seq {s_}", max_abs_tol=3e-3 * float(np.abs(want).max()),
+                                  rel_l2_tol=1.5e-3)
+                    toks[s_] = D.argmaxLast(want, hp.nVocab)
+        finally:
+            batch.close()
+    finally:
+        D.unloadModelBackend()
+
+
 def test_dense_contract_errors():
     hp, _ = CASES["llama_hd64"]
     m = D.random_dense_model(hp, 3)
