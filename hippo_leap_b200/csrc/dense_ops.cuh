@@ -24,6 +24,7 @@ __global__ void embedding_f16_kernel(const __half* __restrict__ table, const int
 // out[t][:] = fp16( x[t][:] * (1 / sqrt(mean(x[t]^2) + eps)) * w[:] ); one block per token row
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                            int dim, float eps, __half* __restrict__ out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a projection queued behind may start loading its weights
   const float* xr = x + static_cast<int64_t>(blockIdx.x) * dim;
   const float inv = block_rms_inv_256(xr, dim, eps);
   __half* orow = out + static_cast<int64_t>(blockIdx.x) * dim;
@@ -33,6 +34,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
 // h[t][f] = fp16( silu(gate) * up ), gate = gu[t][2f], up = gu[t][2f + 1]: the fp16 output of ONE GEMM whose weight
 // rows interleave gate and up
 __global__ void silu_mul_kernel(const __half* __restrict__ gu, int n_ffn, int64_t total, __half* __restrict__ h) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a projection queued behind may start loading its weights
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t t = idx / n_ffn, f = idx % n_ffn;

@@ -770,7 +770,17 @@ static int32_t ensure_splitk(hl_ctx* ctx, size_t floats) {
 }
 static int32_t launch_splitk_reduce(hl_ctx* ctx, const LinearArgs& g, int splits) {
   const int64_t quads = static_cast<int64_t>((g.N + 3) / 4) * g.M;
-  splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, ctx->stream>>>(ctx->splitk_part, splits, g);
+  static const bool no_pdl = getenv("HL_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>((quads + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  HL_CUDA(ctx, cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float*>(ctx->splitk_part), splits, g));
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;
@@ -807,7 +817,18 @@ static int32_t launch_wide(hl_ctx* ctx, const LinearArgs& g) {
   int32_t rc = make_map_2d(ctx, &w_map, g.w, g.N, g.K, g.ldw, Cfg::BW);
   if (rc == HL_OK) rc = make_map_2d(ctx, &a_map, g.a, g.M, g.K, g.lda, p.m_pad);
   if (rc != HL_OK) return rc;
-  linear_wide_kernel<<<dim3(tiles_n, splits), Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(w_map, a_map, p);
+  static const bool no_pdl = getenv("HL_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(tiles_n, splits);
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  HL_CUDA(ctx, cudaLaunchKernelEx(&cfg, linear_wide_kernel, w_map, a_map, p));
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return splits > 1 ? launch_splitk_reduce(ctx, g, splits) : HL_OK;

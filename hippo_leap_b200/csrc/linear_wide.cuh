@@ -28,6 +28,10 @@ struct WideArgs {
 
 // out[m][n] = sum_s part[s][m][n] (+ residual), splits added in index order; four consecutive n per thread.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, LinearArgs g) {
+  // launched with programmatic stream serialisation behind the kernel that writes the partials: resident early, it
+  // waits here for that whole grid; the kernel behind this one may in turn start its own weight loads now
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t quads_per_row = (g.N + 3) >> 2;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (idx >= quads_per_row * g.M) return;
@@ -92,6 +96,10 @@ __global__ void __launch_bounds__(192, 2)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // Launched with programmatic stream serialisation: this grid may become resident while the kernel in front of it
+  // is still running.  W is written by no kernel, so the producer streams its first stages at once; everything that
+  // reads or writes activations (the A loads, the epilogue) first waits for the grids in front (griddepcontrol.wait).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * Cfg::BW;
   const int kb = blockIdx.y * p.kl, ke = min(g.K, kb + p.kl);
@@ -122,9 +130,17 @@ __global__ void __launch_bounds__(192, 2)
     if (lane == 0) {
       tma_prefetch_desc(&w_map);
       tma_prefetch_desc(&a_map);
-      for (int it = 0; it < n_kb; ++it) {
+      const int n_first = n_kb < S ? n_kb : S;
+      for (int it = 0; it < n_first; ++it) {  // W of the first stages, before the grid dependency is resolved
+        mbar_arrive_expect_tx(&full[it], Cfg::kWBytes + a_bytes);
+        tma_load_2d(base + it * Cfg::kStageBytes, &w_map, &full[it], kb + it * Cfg::BK, n0);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int it = 0; it < n_first; ++it)
+        tma_load_2d(base + it * Cfg::kStageBytes + Cfg::kWBytes, &a_map, &full[it], kb + it * Cfg::BK, 0);
+      for (int it = S; it < n_kb; ++it) {
         const int s = it % S;
-        if (it >= S) tc_wait(&empty[s], ((it / S) - 1) & 1, g.status, 780 + s, abort_flag);
+        tc_wait(&empty[s], ((it / S) - 1) & 1, g.status, 780 + s, abort_flag);
         mbar_arrive_expect_tx(&full[s], Cfg::kWBytes + a_bytes);
         const uint32_t dst = base + s * Cfg::kStageBytes;
         tma_load_2d(dst, &w_map, &full[s], kb + it * Cfg::BK, n0);
@@ -153,6 +169,7 @@ __global__ void __launch_bounds__(192, 2)
     const int quad = warp & 3;
     const int n = n0 + quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the residual / output buffers belong to earlier kernels until now
     tc_wait(acc_full, 0, g.status, 795, abort_flag);
     tc_fence_after();
     float* mine = p.splits > 1 ? p.part + static_cast<int64_t>(blockIdx.y) * g.M * g.N : nullptr;
