@@ -53,6 +53,7 @@ SYMBOLS = {
     "hl_b200_attn_prefill": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _i32, _vp, _i32, _view_p, _f32p]),
     "hl_b200_attn_prefill_bcast": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _i32, _vp, _i32, _view_p, C.POINTER(_vp), _i32, _f32p]),
     "hl_b200_attn_decode": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p, _f32p]),
+    "hl_b200_attn_decode_bcast": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p, C.POINTER(_vp), _i32, _f32p]),
     "hl_b200_attn_prefill_gated": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _i32, _vp, _i32, _view_p, _view_p, _f32p]),
     "hl_b200_attn_decode_gated": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p, _view_p, _f32p]),
     "hl_b200_attn_decode_static": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _i32, _vp, _i32, _vp, _i32, _view_p]),

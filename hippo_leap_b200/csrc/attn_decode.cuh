@@ -35,7 +35,22 @@ struct DecodeArgs {
   int32_t rope_dim, rope_mode;
   int32_t block_tokens, num_blocks, max_blocks;
   int32_t chunk_tokens, max_chunks;
+  // Extra destinations of the output rows (same dtype and strides as `out`): the same buffer on peer GPUs, mapped
+  // into this GPU's address space.  With KV heads sharded across GPUs every finished row is stored to all of them
+  // with plain stores over NVLink, so the all-gather of head outputs needs no collective kernel.
+  void* bcast[7];
+  int32_t n_bcast;
 };
+
+// One output element to the local destination and to every broadcast destination.
+__device__ __forceinline__ void decode_store(const DecodeArgs& a, int b, int h, int d, float x) {
+  view_store(a.out, b, h, d, x);
+  for (int i = 0; i < a.n_bcast; ++i) {
+    View o = a.out;
+    o.ptr = a.bcast[i];
+    view_store(o, b, h, d, x);
+  }
+}
 
 template <int HD, int NW, int STAGES>
 struct DecodeCfg {
@@ -63,7 +78,22 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   // prefetches its weights) may start now; it still waits for this whole grid before it reads the attention output
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int ctx = a.ctx_lens[b];
+  // ctx_lens is device data the host cannot see: a value beyond what the grid and the partial slots were sized for
+  // (max_ctx_h) is reported and clamped, so the combine pass never reads past this row's slots; a non-positive one
+  // (decode always attends at least the new token's own key) is reported and the output row is zeroed.
+  int ctx = a.ctx_lens[b];
+  if (ctx > a.max_chunks * a.chunk_tokens) {
+    report(a.status, HL_ERR_BOUNDS, b);
+    ctx = a.max_chunks * a.chunk_tokens;
+  }
+  if (ctx <= 0) {
+    if (chunk == 0) {
+      report(a.status, HL_ERR_BOUNDS, b);
+      for (int idx = threadIdx.x; idx < a.group * HD; idx += blockDim.x)
+        decode_store(a, b, kvh * a.group + idx / HD, idx % HD, 0.f);
+    }
+    return;
+  }
   const int t_begin = chunk * a.chunk_tokens;
   if (t_begin >= ctx) return;  // uniform for the CTA
   const int t_end = min(ctx, t_begin + a.chunk_tokens);
@@ -283,7 +313,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     }
     const int h = kvh * a.group + r;
     if (n_chunks_seq == 1) {
-      view_store(a.out, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
+      decode_store(a, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
     } else {
       const int64_t pi = (static_cast<int64_t>(b) * a.n_head + h) * a.max_chunks + chunk;
       a.part_o[pi * HD + d] = acc;
@@ -302,9 +332,9 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
   // its weight prefetch now; it still waits for this grid to finish before it reads the attention output
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int ctx = a.ctx_lens[b];
+  const int ctx = min(a.ctx_lens[b], a.max_chunks * a.chunk_tokens);  // clamped (and reported) like the decode kernel
   const int n = (ctx + a.chunk_tokens - 1) / a.chunk_tokens;
-  if (n <= 1) return;  // the decode kernel already wrote the final row
+  if (n <= 1) return;  // the decode kernel already wrote the final row (or zeroed it: empty context)
   const int64_t p0 = (static_cast<int64_t>(b) * a.n_head + h) * a.max_chunks;
   float M = -INFINITY;
   for (int ci = 0; ci < n; ++ci) M = fmaxf(M, a.part_ml[(p0 + ci) * 2]);
@@ -314,7 +344,7 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
     L += a.part_ml[(p0 + ci) * 2 + 1] * f;
     acc += a.part_o[(p0 + ci) * HD + d] * f;
   }
-  view_store(a.out, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
+  decode_store(a, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
 }
 
 }  // namespace hl

@@ -89,38 +89,26 @@ extern "C" int32_t hl_b200_attn_decode_static(hl_ctx* ctx, hl_kv* kv, int32_t la
                                               const hl_view* q, int32_t batch, const int32_t* ctx_lens,
                                               int32_t max_ctx_h, const int32_t* block_tables,
                                               int32_t max_blocks_per_seq, const hl_view* out) {
-  if (!ctx) return HL_ERR_ARG;
-  if (!kv || !s || !q || !out || !q->ptr || !out->ptr || !ctx_lens || !block_tables)
-    return hl_fail(ctx, HL_ERR_ARG, "decode_static: null argument");
-  if (layer < 0 || layer >= kv->n_layers) return hl_fail(ctx, HL_ERR_ARG, "decode_static: layer %d outside the pool", layer);
-  if (s->n_head <= 0 || s->n_head_kv <= 0 || s->n_head % s->n_head_kv != 0)
-    return hl_fail(ctx, HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
-  if (s->n_head_kv != kv->n_head_kv || s->head_dim != kv->head_dim || (s->head_dim != 64 && s->head_dim != 128))
-    return hl_fail(ctx, HL_ERR_ARG, "decode_static: shape does not match the KV pool");
-  if (s->n_head / s->n_head_kv > 16) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode_static: n_head / n_head_kv > 16");
-  if (s->rope_dim < 0 || s->rope_dim > s->head_dim || (s->rope_dim & 1) || (s->rope_mode != 0 && s->rope_mode != 1))
-    return hl_fail(ctx, HL_ERR_ARG, "decode_static: bad rope_dim or rope_mode");
-  if (s->rope_dim > 0 && (!ctx->theta_d || ctx->theta_half < s->rope_dim / 2))
-    return hl_fail(ctx, HL_ERR_ARG, "RoPE table not set or shorter than rope_dim/2 (hl_b200_set_rope)");
-  if ((q->dtype != HL_DTYPE_F32 && q->dtype != HL_DTYPE_F16) || (out->dtype != HL_DTYPE_F32 && out->dtype != HL_DTYPE_F16))
-    return hl_fail(ctx, HL_ERR_ARG, "decode_static: dtype is neither f32 nor f16");
-  if (batch <= 0 || batch > 65535 || max_ctx_h <= 0 || max_blocks_per_seq <= 0)
-    return hl_fail(ctx, HL_ERR_ARG, "decode_static: non-positive or oversized batch / context");
+  // The same argument checks as hl_b200_attn_decode, so a bad view comes back as a status code, never as a fault.
+  int32_t rc = hl_check_shape(ctx, kv, s, layer);
+  if (rc == HL_OK) rc = hl_check_view(ctx, q, "q");
+  if (rc == HL_OK) rc = hl_check_view(ctx, out, "out");
+  if (rc != HL_OK) return rc;
+  if (batch <= 0 || batch > 65535) return hl_fail(ctx, HL_ERR_ARG, "decode_static: batch %d outside [1, 65535]", batch);
+  if (!ctx_lens || !block_tables || max_blocks_per_seq <= 0)
+    return hl_fail(ctx, HL_ERR_ARG, "decode_static: null ctx_lens or block table");
+  if (max_ctx_h <= 0) return hl_fail(ctx, HL_ERR_ARG, "decode_static: max_ctx_h must be positive");
   if (static_cast<int64_t>(max_ctx_h) > static_cast<int64_t>(max_blocks_per_seq) * kv->block_tokens)
     return hl_fail(ctx, HL_ERR_CAPACITY, "KV cache full: context %d exceeds the block table", max_ctx_h);
+  if (s->n_head / s->n_head_kv > 16) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode_static: n_head / n_head_kv > 16");
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
-  int32_t rc = static_setup(ctx);
+  rc = static_setup(ctx);
   if (rc != HL_OK) return rc;
 
   hl::DecodeArgs a{};
-  // same chunking rule as hl_b200_attn_decode (about eight CTAs per SM, 64..1024 tokens, or the tuning value)
-  if (ctx->decode_chunk > 0) {
-    a.chunk_tokens = ctx->decode_chunk;
-  } else {
-    int64_t chunk = (static_cast<int64_t>(max_ctx_h) * batch * s->n_head_kv) / (8 * ctx->n_sm);
-    chunk = ((chunk + 63) / 64) * 64;
-    a.chunk_tokens = static_cast<int32_t>(chunk < 64 ? 64 : (chunk > 1024 ? 1024 : chunk));
-  }
+  // the chunking rule of hl_b200_attn_decode itself: both entry points cut a context the same way, so their results
+  // agree in summation order too
+  a.chunk_tokens = hl_decode_chunk_tokens(ctx, batch, s->n_head_kv, max_ctx_h);
   a.max_chunks = (max_ctx_h + a.chunk_tokens - 1) / a.chunk_tokens;
   const size_t need = static_cast<size_t>(batch) * s->n_head * a.max_chunks;
   if (a.max_chunks > 65535 || need > kStaticTriples)

@@ -201,7 +201,12 @@ struct KvRef {
   int table_len;
 };
 
-KvRef ref_of(const hl_kv_cache* cache) { return KvRef{static_cast<hl_kv*>(cache->gpu_cache), d.table_d, d.table_len}; }
+// The identity block table is shared by all caches and only ever grows; each cache uses its own number of blocks
+// as the table length, so a smaller cache created later does not shorten an older cache's view of it.
+KvRef ref_of(const hl_kv_cache* cache) {
+  hl_kv* kv = static_cast<hl_kv*>(cache->gpu_cache);
+  return KvRef{kv, d.table_d, kv->num_blocks};
+}
 
 int32_t forward(const int32_t* tokens_h, int n, int pos0, KvRef ref, bool decode, int grid_ctx = 0,
                 bool from_pinned = false, const BatchDecode* bd = nullptr) {
@@ -586,14 +591,24 @@ extern "C" int32_t hl_dense_init_kv_cache(int32_t device, const hl_dense_hparams
   hl_kv* kv = nullptr;
   D_TRY(hl_b200_kv_create(d.ctx, hp->n_layer, hp->n_head_kv, hp->head_dim, bt, nb, &kv));
   if (d.table_len < nb) {
+    // Grow-only.  A decode graph captured for an older cache has the old table address baked in: the epoch bump
+    // makes the next step of that cache capture again instead of replaying through freed memory.
     if (d.table_d) cudaFree(d.table_d);
     d.table_d = nullptr;
+    d.table_len = 0;
+    d.buf_epoch++;
     std::vector<int32_t> ident(nb);
     for (int i = 0; i < nb; ++i) ident[i] = i;
-    D_CUDA(cudaMalloc(&d.table_d, nb * sizeof(int32_t)));
-    D_CUDA(cudaMemcpy(d.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice));
+    cudaError_t e = cudaMalloc(&d.table_d, nb * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemcpy(d.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      if (d.table_d) cudaFree(d.table_d);
+      d.table_d = nullptr;
+      hl_b200_kv_destroy(d.ctx, kv);
+      return dfail(HL_ERR_CUDA, "block table allocation failed");
+    }
+    d.table_len = nb;
   }
-  d.table_len = nb;
   out->cur_len = 0;
   out->max_len = max_len;
   out->n_head_kv = hp->n_head_kv;

@@ -49,7 +49,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int32_t check_view(hl_ctx* ctx, const hl_view* v, const char* name) {
+}  // namespace
+
+int32_t hl_check_view(hl_ctx* ctx, const hl_view* v, const char* name) {
   if (!v || !v->ptr) return hl_fail(ctx, HL_ERR_ARG, "%s: null view or pointer", name);
   if (v->dtype != HL_DTYPE_F32 && v->dtype != HL_DTYPE_F16)
     return hl_fail(ctx, HL_ERR_ARG, "%s: dtype %d is neither f32 nor f16", name, v->dtype);
@@ -59,11 +61,7 @@ int32_t check_view(hl_ctx* ctx, const hl_view* v, const char* name) {
   return HL_OK;
 }
 
-View to_view(const hl_view* v) {
-  return View{v->ptr, v->dtype, v->tok_stride, v->head_stride, v->dim_stride};
-}
-
-int32_t check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_t layer) {
+int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_t layer) {
   if (!ctx) return HL_ERR_ARG;
   if (!kv || !s) return hl_fail(ctx, HL_ERR_ARG, "null kv or shape");
   if (layer < 0 || layer >= kv->n_layers)
@@ -84,6 +82,12 @@ int32_t check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_
   return HL_OK;
 }
 
+namespace {
+View to_view(const hl_view* v) { return View{v->ptr, v->dtype, v->tok_stride, v->head_stride, v->dim_stride}; }
+inline int32_t check_view(hl_ctx* ctx, const hl_view* v, const char* name) { return hl_check_view(ctx, v, name); }
+inline int32_t check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_t layer) {
+  return hl_check_shape(ctx, kv, s, layer);
+}
 }  // namespace
 
 int32_t hl_begin_timing(hl_ctx* ctx, float* gpu_ms) {
@@ -474,7 +478,8 @@ int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_
 
 static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* q,
                            int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h, const int32_t* block_tables,
-                           int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out, float* gpu_ms) {
+                           int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out, float* gpu_ms,
+                           void* const* bcast = nullptr, int32_t n_bcast = 0) {
   int32_t rc = check_shape(ctx, kv, s, layer);
   if (rc == HL_OK) rc = check_view(ctx, q, "q");
   if (rc == HL_OK) rc = check_view(ctx, out, "out");
@@ -528,6 +533,8 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
   a.block_tokens = kv->block_tokens;
   a.num_blocks = kv->num_blocks;
   a.max_blocks = max_blocks_per_seq;
+  a.n_bcast = n_bcast;
+  for (int i = 0; i < n_bcast; ++i) a.bcast[i] = bcast[i];
 
   rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
@@ -552,6 +559,24 @@ extern "C" int32_t hl_b200_attn_decode_gated(hl_ctx* ctx, hl_kv* kv, int32_t lay
   if (ctx && !gate) return hl_fail(ctx, HL_ERR_ARG, "decode_gated: null gate view");
   return decode_impl(ctx, kv, layer, s, q, batch, ctx_lens, max_ctx_h, block_tables, max_blocks_per_seq, gate, out,
                      gpu_ms);
+}
+
+extern "C" int32_t hl_b200_attn_decode_bcast(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s,
+                                             const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                                             int32_t max_ctx_h, const int32_t* block_tables,
+                                             int32_t max_blocks_per_seq, const hl_view* out,
+                                             void* const* peer_out_ptrs, int32_t n_peers, float* gpu_ms) {
+  if (!ctx) return HL_ERR_ARG;
+  if (n_peers < 0 || n_peers > 7) return hl_fail(ctx, HL_ERR_ARG, "decode_bcast: n_peers %d outside [0, 7]", n_peers);
+  if (n_peers > 0 && !peer_out_ptrs) return hl_fail(ctx, HL_ERR_ARG, "decode_bcast: null peer pointer list");
+  const size_t el = out && out->dtype == HL_DTYPE_F16 ? 2 : 4;
+  for (int i = 0; i < n_peers; ++i) {
+    if (!peer_out_ptrs[i]) return hl_fail(ctx, HL_ERR_ARG, "decode_bcast: null peer pointer %d", i);
+    if (reinterpret_cast<uintptr_t>(peer_out_ptrs[i]) % el)
+      return hl_fail(ctx, HL_ERR_ALIGN, "decode_bcast: peer pointer %d not aligned to the output element size", i);
+  }
+  return decode_impl(ctx, kv, layer, s, q, batch, ctx_lens, max_ctx_h, block_tables, max_blocks_per_seq, nullptr, out,
+                     gpu_ms, peer_out_ptrs, n_peers);
 }
 
 // ---------------------------------------------------------------------------------------------

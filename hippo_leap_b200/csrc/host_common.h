@@ -48,6 +48,13 @@ struct hl_kv {
 
 int32_t hl_fail(hl_ctx* ctx, int32_t code, const char* fmt, ...);
 
+// Argument checks shared by every attention entry point (defined in hl_b200.cu): the shape against the KV pool and
+// the RoPE table; a view's pointer (non-null, aligned to its element size) and dtype.
+int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int32_t layer);
+int32_t hl_check_view(hl_ctx* ctx, const hl_view* v, const char* name);
+// Tokens per split-KV chunk of a decode launch: the tuning value, or about eight CTAs per SM within 128..1024.
+int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_kv, int32_t max_ctx);
+
 // Decode projection (linear_gemv.cuh), 1 <= M <= 4.  mode 0: a = fp16 rows; mode 1: a = fp32 rows (lda in floats),
 // RMSNorm with norm_w fused in front.  swiglu != 0: W rows interleave gate / up, out[M][N / 2] = fp16 silu(gate) * up.
 int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const void* a, int64_t lda, const float* norm_w,

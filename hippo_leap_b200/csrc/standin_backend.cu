@@ -224,11 +224,11 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
     hl_view qv{g.q, HL_DTYPE_F32, qd, g.hp.head_dim, 1}, kv_{g.k, HL_DTYPE_F32, kd, g.hp.head_dim, 1},
         vv{g.v, HL_DTYPE_F32, kd, g.hp.head_dim, 1}, ov{g.out + l * layer_stride, HL_DTYPE_F32, qd, g.hp.head_dim, 1};
     if (decode) {
-      B_TRY(hl_b200_kv_append_batch(g.ctx, kv, l, &s, &kv_, &vv, 1, g.ctx_len_d, g.table_d, g.table_len));
-      B_TRY(hl_b200_attn_decode(g.ctx, kv, l, &s, &qv, 1, g.ctx_len_d, grid_ctx, g.table_d, g.table_len, &ov, nullptr));
+      B_TRY(hl_b200_kv_append_batch(g.ctx, kv, l, &s, &kv_, &vv, 1, g.ctx_len_d, g.table_d, kv->num_blocks));
+      B_TRY(hl_b200_attn_decode(g.ctx, kv, l, &s, &qv, 1, g.ctx_len_d, grid_ctx, g.table_d, kv->num_blocks, &ov, nullptr));
     } else {
-      B_TRY(hl_b200_kv_append_seq(g.ctx, kv, l, &s, &kv_, &vv, n, pos0, g.table_d, g.table_len));
-      B_TRY(hl_b200_attn_prefill(g.ctx, kv, l, &s, &qv, n, pos0, g.table_d, g.table_len, &ov, nullptr));
+      B_TRY(hl_b200_kv_append_seq(g.ctx, kv, l, &s, &kv_, &vv, n, pos0, g.table_d, kv->num_blocks));
+      B_TRY(hl_b200_attn_prefill(g.ctx, kv, l, &s, &qv, n, pos0, g.table_d, kv->num_blocks, &ov, nullptr));
     }
   }
   const int threads = 256;
@@ -274,14 +274,24 @@ extern "C" int32_t hl_backend_init_kv_cache(int32_t device, const hl_hparams* hp
   hl_kv* kv = nullptr;
   B_TRY(hl_b200_kv_create(g.ctx, hp->n_layer, hp->n_head_kv, hp->head_dim, bt, nb, &kv));
   if (g.table_len < nb) {
+    // Grow-only identity table shared by all caches (each uses its own number of blocks as the length).  A decode
+    // graph captured for an older cache has the old address baked in: the epoch bump makes it capture again.
     if (g.table_d) cudaFree(g.table_d);
     g.table_d = nullptr;
+    g.table_len = 0;
+    g.buf_epoch++;
     std::vector<int32_t> ident(nb);
     for (int i = 0; i < nb; ++i) ident[i] = i;
-    B_CUDA(cudaMalloc(&g.table_d, nb * sizeof(int32_t)));
-    B_CUDA(cudaMemcpy(g.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice));
+    cudaError_t e = cudaMalloc(&g.table_d, nb * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemcpy(g.table_d, ident.data(), nb * sizeof(int32_t), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      if (g.table_d) cudaFree(g.table_d);
+      g.table_d = nullptr;
+      hl_b200_kv_destroy(g.ctx, kv);
+      return bfail(HL_ERR_CUDA, "block table allocation failed");
+    }
+    g.table_len = nb;
   }
-  g.table_len = nb;
   out->cur_len = 0;
   out->max_len = max_len;
   out->n_head_kv = hp->n_head_kv;

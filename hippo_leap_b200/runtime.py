@@ -281,6 +281,19 @@ class Context:
             C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
 
+    def attn_decode_bcast(self, kv: KvPool, layer: int, shape: AttnShape, q, ctx_lens: torch.Tensor, max_ctx: int,
+                          block_tables: torch.Tensor, out: torch.Tensor, peer_ptrs, timed: bool = False):
+        """hl_b200_attn_decode_bcast: the decode step whose kernels also store each output row to ``peer_ptrs``
+        (device addresses of the same output slice on other GPUs)."""
+        sc, qc, oc = shape.c(), view_of(q), view_of(out)
+        arr = (C.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
+        ms = C.c_float(0.0)
+        self._check(self.lib.hl_b200_attn_decode_bcast(
+            self.handle, kv.handle, layer, C.byref(sc), C.byref(qc), q.shape[0], _i32_dev(ctx_lens), max_ctx,
+            _i32_dev(block_tables), block_tables.shape[1], C.byref(oc), arr, len(peer_ptrs),
+            C.byref(ms) if timed else None))
+        return (out, ms.value) if timed else out
+
     def linear_f16(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
                    resid: torch.Tensor | None = None, out_dtype=torch.float32, timed: bool = False):
         """out[M, N] = a[M, K] @ w[N, K].T (+ resid): fp16 inputs, fp32 accumulation (hl_b200_linear_f16)."""

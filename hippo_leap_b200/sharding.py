@@ -4,7 +4,9 @@ Two natural splits exist and nothing else is invented:
   * independent decode sequences -> ranks, no collective (``shard_sequences``);
   * KV-head groups -> ranks for prefill / batched decode of one sequence set: rank r owns KV heads
     [r*Hkv/N, (r+1)*Hkv/N) and the query heads that map onto them; each rank writes its output
-    head-major, so ONE all-gather in rank order yields the final [n_head][n_tok][head_dim] tensor.
+    head-major, so ONE all-gather in rank order yields the final [n_head][n_tok][head_dim] tensor
+    (``HeadShardedPrefill`` / ``FusedHeadShardedPrefill`` for prefill, ``HeadShardedDecode`` /
+    ``FusedHeadShardedDecode`` for a batched decode step).
 The reference has no multi-GPU code at all (one stream, one global lock:
 src/hippo_leap/backends/naive.nim:237-243, src/hippo_leap/inference.nim:53-54).
 """
@@ -152,4 +154,65 @@ class FusedHeadShardedPrefill:
                                     self.peer_ptrs)
         if self.hdl is not None:
             self.hdl.barrier()  # every rank's kernel has finished: all slices of `full` are in place
+        return self.full
+
+
+class HeadShardedDecode:
+    """One batched decode step with KV heads split across ranks and ONE all-gather of the head outputs.
+
+    Rank r holds KV heads [r*Hkv/N, (r+1)*Hkv/N) of EVERY sequence's pages (same block tables on all ranks, a pool
+    with Hkv/N heads) and runs the split-KV decode on the n_head/N query heads that map onto them -- N copies of the
+    reference's single-GPU gpuAttentionDecode (src/hippo_leap/backends/naive.nim:4714-4717), each over 1/N of the cache
+    bytes.  Output is head-major ``[n_head/N][batch][head_dim]``, so the rank-order concatenation of one
+    ``all_gather_into_tensor`` is the final ``[n_head][batch][head_dim]``.  ``shape`` is the LOCAL shape.
+    """
+
+    def __init__(self, ctx, kv, shape, batch: int, device, world: int | None = None, dtype=torch.float32):
+        self.ctx, self.kv, self.shape, self.batch = ctx, kv, shape, batch
+        self.world = world if world is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+        self.local = torch.empty((shape.n_head, batch, shape.head_dim), dtype=dtype, device=device)
+        self.full = torch.empty((shape.n_head * self.world, batch, shape.head_dim), dtype=dtype, device=device)
+
+    def run(self, q, k_new, v_new, ctx_lens, max_ctx: int, block_tables, layer: int = 0) -> torch.Tensor:
+        """q [batch, n_head_local, hd], k_new / v_new [batch, n_head_kv_local, hd]: this rank's heads of the new token
+        of every sequence (in a full model they come from column-sharded projections).  Appends, attends, gathers."""
+        self.ctx.kv_append_batch(self.kv, layer, self.shape, k_new, v_new, ctx_lens, block_tables)
+        self.ctx.attn_decode(self.kv, layer, self.shape, q, ctx_lens, max_ctx, block_tables, self.local.permute(1, 0, 2))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.full, self.local)
+        else:
+            self.full.copy_(self.local)
+        return self.full
+
+
+class FusedHeadShardedDecode:
+    """The same step with the gather fused into the decode kernels: the full ``[n_head][batch][head_dim]`` result
+    lives in symmetric memory and every rank's decode / combine kernel stores its finished rows into its head slice
+    on ALL ranks (plain stores to peer memory over NVLink).  No collective kernel runs; a barrier remains."""
+
+    def __init__(self, ctx, kv, shape, batch: int, n_head_total: int, device, group=None, dtype=torch.float32):
+        import torch.distributed._symmetric_memory as symm
+
+        self.ctx, self.kv, self.shape, self.batch = ctx, kv, shape, batch
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        hd = shape.head_dim
+        if self.world > 1:
+            self.full = symm.empty((n_head_total, batch, hd), dtype=dtype, device=device)
+            self.hdl = symm.rendezvous(self.full, group if group is not None else dist.group.WORLD)
+            ptrs = list(self.hdl.buffer_ptrs)
+        else:
+            self.full = torch.empty((n_head_total, batch, hd), dtype=dtype, device=device)
+            self.hdl, ptrs = None, [self.full.data_ptr()]
+        q_lo = self.rank * shape.n_head
+        self.local = self.full[q_lo:q_lo + shape.n_head]
+        byte_off = q_lo * batch * hd * self.full.element_size()
+        self.peer_ptrs = [ptrs[p] + byte_off for p in range(self.world) if p != self.rank]
+
+    def run(self, q, k_new, v_new, ctx_lens, max_ctx: int, block_tables, layer: int = 0) -> torch.Tensor:
+        self.ctx.kv_append_batch(self.kv, layer, self.shape, k_new, v_new, ctx_lens, block_tables)
+        self.ctx.attn_decode_bcast(self.kv, layer, self.shape, q, ctx_lens, max_ctx, block_tables,
+                                   self.local.permute(1, 0, 2), self.peer_ptrs)
+        if self.hdl is not None:
+            self.hdl.barrier()  # every rank's kernels have finished: all slices of `full` are in place
         return self.full

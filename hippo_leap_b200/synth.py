@@ -120,6 +120,14 @@ def shard_longest_first(ctx_lens: np.ndarray, n_ranks: int):
     return [sorted(o) for o in owner]
 
 
+def gen_sharded_ctx_lens(cfg: AttnConfig, world: int):
+    """The batched-decode workload at ``world`` GPUs: ONE seeded set of ``cfg.batch * world`` sequences (its first
+    ``cfg.batch`` values are the one-GPU set), assigned to ranks greedy longest-first so that every rank streams
+    about the same number of KV bytes.  Returns (all context lengths, list of per-rank index lists)."""
+    all_ctx = gen_ctx_lens(cfg, batch=cfg.batch * world)
+    return all_ctx, shard_longest_first(all_ctx, world)
+
+
 def prefill_flops(n_head: int, head_dim: int, n_tok: int, start_pos: int = 0) -> float:
     """4 * hd * n_head * (causal pairs): QK^T and PV, 2 flop per MAC."""
     pairs = n_tok * start_pos + n_tok * (n_tok + 1) / 2

@@ -164,11 +164,27 @@ int32_t hl_b200_attn_prefill_bcast(hl_ctx* ctx, hl_kv* kv, int32_t layer, const 
  * ctx_lens[i] cached keys (the new token's own K/V included: curLen = pos + 1).
  * Split-KV: the context is cut into chunks that run in parallel and a second pass merges
  * the partial (max, sum, out) triples.  max_ctx_h >= max_i ctx_lens[i] (host value, sizes
- * the grid and the scratch). */
+ * the grid and the scratch).  A device-side ctx_lens[i] beyond max_ctx_h rounded up to whole
+ * chunks, or <= 0, sets the device status word to HL_ERR_BOUNDS (detail = i); the context is
+ * clamped to the grid (resp. the output row zeroed) and nothing is read out of range. */
 int32_t hl_b200_attn_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
                             const hl_view* q, int32_t batch, const int32_t* ctx_lens,
                             int32_t max_ctx_h, const int32_t* block_tables,
                             int32_t max_blocks_per_seq, const hl_view* out, float* gpu_ms);
+
+/* No counterpart in the reference (which has no multi-GPU code).  hl_b200_attn_decode whose kernels ALSO store
+ * every output row to up to 7 more destinations with the layout of `out`: the same buffer on peer GPUs, mapped
+ * into this GPU's address space.  With KV heads sharded across GPUs (each GPU holds its KV heads of every
+ * sequence's pages and runs the decode step on the query heads that map onto them), each GPU passes as `out` its
+ * own head slice of the full [n_head][batch][head_dim] buffer and as peers the same slice of every other GPU's
+ * buffer: the single all-gather of per-head outputs that replaces N copies of gpuAttentionDecode
+ * (naive.nim:4714-4717) then happens inside the decode step's own stores.  Peers must be synchronised by the
+ * caller before they read (a barrier after the call's stream work has completed on every rank). */
+int32_t hl_b200_attn_decode_bcast(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* shape,
+                                  const hl_view* q, int32_t batch, const int32_t* ctx_lens,
+                                  int32_t max_ctx_h, const int32_t* block_tables,
+                                  int32_t max_blocks_per_seq, const hl_view* out,
+                                  void* const* peer_out_ptrs, int32_t n_peers, float* gpu_ms);
 
 /* The two attention calls with the output gate of the qwen3.5-MoE attention layers fused into
  * their epilogue: out <- sigmoid(gate) * out, replacing gpuAttnGate (naive.nim:2287-2300, applied at
@@ -191,7 +207,7 @@ int32_t hl_b200_attn_decode_gated(hl_ctx* ctx, hl_kv* kv, int32_t layer, const h
  * cudaMalloc / cudaFree inside the decode loop.  Same arguments and result as hl_b200_attn_decode
  * (no gpu_ms); the split-KV partials live in a fixed 16.25 MiB array inside the library image, held
  * by every GPU that loads the library until the process exits.  Limit: batch * n_head * chunks <=
- * 32768 partial slots (chunks = ceil(max_ctx_h / chunk_tokens), 64..1024 tokens per chunk); beyond it
+ * 32768 partial slots (chunks = ceil(max_ctx_h / chunk_tokens), 128..1024 tokens per chunk unless tuned); beyond it
  * the call returns HL_ERR_CAPACITY and launches nothing.  All calls on one GPU share the array: calls
  * whose kernels overlap on the GPU race, so serialise them.  The first call on each device resolves
  * the array's device address and configures the kernel; make it before any stream capture starts. */

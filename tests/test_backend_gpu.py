@@ -258,3 +258,47 @@ def test_decode_graph_is_recaptured_when_a_longer_prompt_grows_the_buffers():
     finally:
         B.freeKvCache(cache)
         B.unloadModelBackend()
+
+
+def test_an_older_cache_survives_larger_and_smaller_caches_created_after_it():
+    """All caches share one grow-only identity block table.  A larger cache re-allocates it: the decode graph captured
+    for the older cache must not replay through the freed table.  A smaller cache must not shorten the older cache's
+    view of the table: a prompt past the smaller cache's capacity still fits the older one."""
+    hp = B.HParams(nVocab=512, nLayer=2, nHead=8, nHeadKv=2, headDim=64)
+    m = B.standin_model(hp, 21)
+    cache_a = B.initKvCache(hp, 400)
+    B.loadModelBackend(m, hp)
+    others = []
+    try:
+        prompt = np.random.Generator(np.random.PCG64([21, 1])).integers(0, hp.nVocab, 90).astype(np.int32)
+        B.setDecodeGraph(False)
+        want = B.generate(m, cache_a, prompt, 40).tokens
+        B.setDecodeGraph(True)
+        cache_a.curLen = 0
+        tok = B.argmaxLast(B.forwardPrefill(m, prompt, cache_a), hp.nVocab)
+        got = [tok]
+        for _ in range(19):
+            tok = B.forwardDecodeToken(m, tok, cache_a)
+            got.append(tok)
+        others.append(B.initKvCache(hp, 3000))          # larger: the shared table is re-allocated
+        for _ in range(20):
+            tok = B.forwardDecodeToken(m, tok, cache_a)  # graph of cache A must have been captured again
+            got.append(tok)
+        assert got == want[:40]
+        others.append(B.initKvCache(hp, 64))            # smaller: 4 blocks
+        long_prompt = np.random.Generator(np.random.PCG64([21, 2])).integers(0, hp.nVocab, 300).astype(np.int32)
+        ref = OracleModel(m, 400, hp.ropeMode)
+        cache_a.curLen = 0
+        logits, ref_logits = B.forwardPrefill(m, long_prompt, cache_a), ref.forward(long_prompt)
+        assert_parity(logits, ref_logits, "prefill past the smaller cache's capacity",
+                      max_abs_tol=2e-3 * float(np.abs(ref_logits).max()), rel_l2_tol=1e-3)
+        tok = B.argmaxLast(ref_logits, hp.nVocab)
+        got_tok, ref_next = B.forwardDecodeToken(m, tok, cache_a), ref.forward([tok])
+        top2 = np.sort(ref_next[0])[-2:]
+        assert got_tok == B.argmaxLast(ref_next, hp.nVocab) or top2[1] - top2[0] < 1e-3 * float(np.abs(ref_next).max())
+    finally:
+        B.setDecodeGraph(True)
+        for c in others:
+            B.freeKvCache(c)
+        B.freeKvCache(cache_a)
+        B.unloadModelBackend()

@@ -349,6 +349,49 @@ def test_decode_graphs_are_recaptured_when_buffers_grow():
         D.unloadModelBackend()
 
 
+def test_dense_older_cache_survives_larger_and_smaller_caches_created_after_it():
+    """The identity block table is shared and grow-only: a larger cache re-allocates it (the older cache's decode graph
+    must be captured again, not replayed through freed memory), a smaller one must not shorten the older cache's view."""
+    hp, qk_norm = CASES["llama_hd64"]
+    m = D.random_dense_model(hp, 61, qk_norm)
+    g = np.random.Generator(np.random.PCG64([61, 1]))
+    max_len = 420
+    D.setDecodeGraph(True)
+    cache_a = D.initKvCache(hp, max_len)
+    D.loadModelBackend(m, hp)
+    others = []
+    try:
+        ref = OracleDense(m, max_len, True)
+        prompt = g.integers(0, hp.nVocab, 40).astype(np.int32)
+        cache_a.curLen = 0
+        want = ref.forward(prompt)
+        assert_parity(D.forwardPrefill(m, prompt, cache_a), want, "prefill", max_abs_tol=3e-3 * float(np.abs(want).max()),
+                      rel_l2_tol=1.5e-3)
+        tok = D.argmaxLast(want, hp.nVocab)
+        for step in range(8):
+            if step == 4:
+                others.append(D.initKvCache(hp, 4000))   # larger: the shared table moves
+            got, want = D.forwardDecode(m, tok, cache_a), ref.forward([tok])
+            assert_parity(got, want, f"decode step {step}", max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
+            tok = D.argmaxLast(want, hp.nVocab)
+        others.append(D.initKvCache(hp, 100))            # smaller: one 128-token block
+        long_ = g.integers(0, hp.nVocab, 300).astype(np.int32)
+        cache_a.curLen = 0
+        for c in ref.caches:
+            c.cur_len = 0
+        want = ref.forward(long_)
+        assert_parity(D.forwardPrefill(m, long_, cache_a), want, "prefill past the smaller cache's capacity",
+                      max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
+        tok = D.argmaxLast(want, hp.nVocab)
+        got, want = D.forwardDecode(m, tok, cache_a), ref.forward([tok])
+        assert_parity(got, want, "decode after it", max_abs_tol=3e-3 * float(np.abs(want).max()), rel_l2_tol=1.5e-3)
+    finally:
+        for c in others:
+            D.freeKvCache(c)
+        D.freeKvCache(cache_a)
+        D.unloadModelBackend()
+
+
 def test_dense_contract_errors():
     hp, _ = CASES["llama_hd64"]
     m = D.random_dense_model(hp, 3)

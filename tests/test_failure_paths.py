@@ -137,3 +137,47 @@ def test_host_side_argument_matrix_on_a_live_context(hl_ctx):
     refuse(L.HL_ERR_ARG, lambda: hl_ctx.attn_decode(kv, 0, shape, tq.to(torch.float64), tctx, 40, ttab))
     assert hl_ctx.launch_count() == launches, "a refused call must not launch anything"
     kv.destroy()
+
+
+@pytest.mark.gpu
+def test_device_side_context_length_beyond_the_grid_reports_bounds(hl_ctx, request):
+    """ctx_lens lives on the device; the host sizes the grid and the partial slots from max_ctx_h.  A context longer
+    than that (a stale host value, a caller mistake) is reported through the status word and clamped to the grid, an
+    empty one is reported and its output row zeroed -- no read outside the partial slots, the context stays usable."""
+    request.node.add_marker("expects_device_status")
+    import torch
+
+    import hippo_leap_b200 as hl
+    hd, H, Hkv, bt = 128, 8, 2, 16
+    ctxs = np.array([600, 130], np.int32)
+    g = np.random.Generator(np.random.PCG64(31))
+    hl_ctx.set_rope(hl.theta_table(hd, 1e4))
+    shape = hl.AttnShape(H, Hkv, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+    nb = (int(ctxs.max()) + bt - 1) // bt
+    kv = hl_ctx.kv_create(1, Hkv, hd, bt, 2 * nb)
+    tables = np.arange(2 * nb, dtype=np.int32).reshape(2, nb)
+    ttab, tctx = torch.from_numpy(tables).cuda(), torch.from_numpy(ctxs).cuda()
+    for i, c in enumerate(ctxs):
+        k = torch.from_numpy(g.standard_normal((int(c), Hkv, hd), dtype=np.float32)).cuda()
+        hl_ctx.kv_append_seq(kv, 0, shape, k, k, 0, ttab[i].contiguous())
+    q = torch.from_numpy(g.standard_normal((2, H, hd), dtype=np.float32)).cuda()
+    hl_ctx.set_tuning(128, 0)
+    try:
+        good = hl_ctx.attn_decode(kv, 0, shape, q, tctx, 600, ttab).clone()
+        assert hl_ctx.device_status() == (0, 0)
+        # max_ctx_h understated by more than one chunk: 3 chunks of 128 on the grid, sequence 0 has 600 keys
+        out = hl_ctx.attn_decode(kv, 0, shape, q, tctx, 384, ttab)
+        assert hl_ctx.device_status() == (L.HL_ERR_BOUNDS, 0)
+        assert torch.isfinite(out).all()
+        assert torch.equal(out[1], good[1])      # the sequence that fits is untouched
+        # an empty context: reported, output row zeroed
+        empty = torch.tensor([0, 130], dtype=torch.int32, device="cuda")
+        out = torch.full_like(good, float("nan"))
+        hl_ctx.attn_decode(kv, 0, shape, q, empty, 600, ttab, out)
+        assert hl_ctx.device_status() == (L.HL_ERR_BOUNDS, 0)
+        assert float(out[0].abs().max()) == 0.0 and torch.equal(out[1], good[1])
+        again = hl_ctx.attn_decode(kv, 0, shape, q, tctx, 600, ttab)
+        assert torch.equal(again, good) and hl_ctx.device_status() == (0, 0)
+    finally:
+        hl_ctx.set_tuning(0, 0)
+        kv.destroy()

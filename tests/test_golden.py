@@ -44,12 +44,14 @@ def _base(name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", NAMES)
-@pytest.mark.parametrize("kernel", [1, 2], ids=["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tcgen05", "tcgen05-pair"])
 def test_cuda_path_matches_golden(hl_ctx, name, kernel):
     import torch
 
     import hippo_leap_b200 as hl
     S, H, Hkv, hd, mode, qw, kw, steps = _case(name)
+    if kernel == 3 and hd != 128:
+        pytest.skip("the SM-pair kernel is built for head_dim 128")
     q, k, v, theta = (GOLD[f"{name}/{x}"] for x in ("q", "k", "v", "theta"))
     hl_ctx.set_rope(theta)
     shape = hl.AttnShape(H, Hkv, hd, hd, mode, 1e-6, None if qw is None else torch.from_numpy(qw).cuda(),

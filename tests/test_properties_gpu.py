@@ -22,7 +22,7 @@ def _shape_for(cfg, rope_mode, qw=None, kw=None):
                         None if kw is None else torch.from_numpy(kw).cuda())
 
 
-@pytest.mark.parametrize("ci,S,kernel", [(2, 2048, 1), (2, 2048, 2), (3, 8192, 2), (5, 32768, 2), (5, 4096, 1)])
+@pytest.mark.parametrize("ci,S,kernel", [(2, 2048, 1), (2, 2048, 2), (3, 8192, 2), (3, 8192, 3), (5, 32768, 2), (5, 32768, 3), (5, 4096, 1)])
 def test_prefill_row_sampled_parity_at_config_sizes(hl_ctx, ci, S, kernel):
     """Configs 2, 3 and 5 at their full prompt lengths (one layer): 48 seeded (token, head) rows are
     checked against the oracle, which computes exactly those rows."""

@@ -42,6 +42,24 @@ def _worker(rank, world, port, q):
         full = sharding.gather_heads(head_major)
         want = oracle.attn_forward(qa, ka, va, oracle.SeqCache(S, Hkv, hd), theta=theta, rope_mode=1, n_threads=1)
         ok_gather = bool(np.array_equal(full.numpy(), want.transpose(1, 0, 2)))
+        # one batched decode step, head-sharded: every rank holds its KV heads of EVERY sequence, attends with its query
+        # heads, and one all-gather of the head-major rows gives the unsharded step
+        ctxs = [5, 17, 9]
+        qd = g.standard_normal((len(ctxs), 1, H, hd), dtype=np.float32)
+        loc, ref = [], []
+        for i, c in enumerate(ctxs):
+            kk = g.standard_normal((c, Hkv, hd), dtype=np.float32)
+            vv = g.standard_normal((c, Hkv, hd), dtype=np.float32)
+            for lo_q, hi_q, lo_kv, hi_kv, dst in ((sh.q_lo, sh.q_hi, sh.kv_lo, sh.kv_hi, loc), (0, H, 0, Hkv, ref)):
+                sc = oracle.SeqCache(c, hi_kv - lo_kv, hd)
+                if c > 1:
+                    oracle.attn_forward(np.zeros((c - 1, hi_q - lo_q, hd), np.float32), kk[:-1, lo_kv:hi_kv],
+                                        vv[:-1, lo_kv:hi_kv], sc, theta=theta, rope_mode=1, rows=[[0, 0]], n_threads=1)
+                dst.append(oracle.attn_forward(qd[i][:, lo_q:hi_q], kk[-1:, lo_kv:hi_kv], vv[-1:, lo_kv:hi_kv], sc,
+                                               theta=theta, rope_mode=1, n_threads=1)[0])
+        dec_local = torch.from_numpy(np.ascontiguousarray(np.stack(loc).transpose(1, 0, 2)))  # [H/N, B, hd]
+        ok_gather = ok_gather and bool(np.array_equal(sharding.gather_heads(dec_local).numpy(),
+                                                      np.stack(ref).transpose(1, 0, 2)))
         # sequence sharding: identical on every rank, disjoint, complete
         ctx = g.integers(512, 8193, 64)
         owners = sharding.shard_sequences(ctx, world)
@@ -87,3 +105,17 @@ def test_head_shard_arithmetic_and_errors():
         sharding.head_shard(0, 3, 64, 8)
     with pytest.raises(ValueError):
         sharding.head_shard(0, 2, 6, 4)
+
+
+def test_sharded_decode_workload_is_one_seeded_set_balanced_by_bytes():
+    sys.path.insert(0, ROOT)
+    from hippo_leap_b200 import synth
+    cfg = synth.CONFIGS[4]
+    one, owners1 = synth.gen_sharded_ctx_lens(cfg, 1)
+    assert np.array_equal(one, synth.gen_ctx_lens(cfg)) and owners1 == [list(range(cfg.batch))]
+    for world in (2, 4, 8):
+        all_ctx, owners = synth.gen_sharded_ctx_lens(cfg, world)
+        assert np.array_equal(all_ctx[:cfg.batch], one)          # the one-GPU set is a prefix of every larger set
+        assert sorted(i for o in owners for i in o) == list(range(cfg.batch * world))
+        loads = np.array([int(all_ctx[o].sum()) for o in owners])
+        assert loads.max() / loads.mean() < 1.01                 # KV bytes per rank within 1 % of the mean
