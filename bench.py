@@ -10,8 +10,9 @@ sequence: KV append + split-KV attention + combine, for one attention layer.  Th
   python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
   python bench.py --impl reference ...                     (CPU oracle on the host cores)
 
-With N > 1 every rank owns its own 64 sequences (weak scaling, no collective on the data path);
-the timed region is bracketed by a barrier + synchronize and the maximum over ranks is reported.
+With N > 1 ONE seeded set of 64 * N sequences is dealt to the ranks greedy longest-first, so every rank streams
+about the same number of KV bytes (weak scaling, no collective on the data path); every timed region is bracketed
+by a barrier + synchronize, the maximum over ranks is taken, and the median of several such regions is reported.
 One JSON line is printed by rank 0.
 """
 from __future__ import annotations
@@ -30,6 +31,7 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
+NCU_DECODE_TRAFFIC_RATIO = 1006.9 / 997.376  # ncu DRAM traffic / algorithmic bytes of the decode + combine launch
 METRIC = "decode_attn_tok_per_s"
 UNIT = "tok/s"
 
@@ -70,7 +72,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
@@ -79,27 +81,30 @@ class ClockSampler:
             try:
                 sm.append(float(f[0]))
                 mx.append(float(f[1]))
+                pw.append(float(f[2]))
             except ValueError:
                 continue
             for n, val in zip(names, f[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w": statistics.median(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------
-def setup_decode(ctx, cfg, rank, device):
-    """Paged pools filled (through the append kernel) with seeded N(0,1) K/V for `cfg.batch`
-    sequences; returns everything a decode step needs."""
+def setup_decode(ctx, cfg, rank, world, device):
+    """This rank's share of the ONE seeded set of `cfg.batch * world` sequences (greedy longest-first on context
+    length: equal KV bytes per rank); paged pools filled (through the append kernel) with seeded N(0,1) K/V;
+    returns everything a decode step needs.  At world 1 the share is the whole 64-sequence set."""
     import torch
 
     import hippo_leap_b200 as hl
     from hippo_leap_b200 import synth
 
-    ctx_lens = synth.gen_ctx_lens(cfg, rank=rank)
+    all_ctx, owners = synth.gen_sharded_ctx_lens(cfg, world)
+    ctx_lens = all_ctx[owners[rank]]
     tables, num_blocks = synth.gen_block_tables(ctx_lens, cfg.block_tokens, cfg.seed + rank)
     shape = hl.AttnShape(cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
     ctx.set_rope(cfg.theta())
@@ -120,17 +125,17 @@ def setup_decode(ctx, cfg, rank, device):
     tctx = torch.from_numpy(ctx_lens).to(device)
     ctx.sync()
     return dict(shape=shape, kv=kv, ctx_lens=ctx_lens, tctx=tctx, ttab=ttab, q=q, kn=kn, vn=vn, out=out,
-                max_ctx=int(ctx_lens.max()))
+                max_ctx=int(ctx_lens.max()), total_sequences=int(len(all_ctx)))
 
 
 def cpu_decode_sample(cfg, n_seq, steps, n_threads):
     """The CPU oracle on the first n_seq sequences of the same seeded workload: `steps` decode steps.
     Returns seconds per step."""
     import oracle
-    from hippo_leap_b200 import synth
+    from hippo_leap_b200 import synth  # workload shapes and seeds only: nothing here loads the CUDA library
 
     ctx_lens = synth.gen_ctx_lens(cfg, rank=0)[:n_seq]
-    theta = cfg.theta()
+    theta = oracle.theta_table(cfg.head_dim, cfg.rope_base)
     g = np.random.Generator(np.random.PCG64(77))
     caches = []
     for c in ctx_lens:
@@ -171,13 +176,21 @@ def run_reference(args, rank, world, result_out):
     value = n_seq * args.steps / t
     sample = (f"first {n_seq} of the 64 seeded sequences (ctx sum {int(ctx_lens.sum())}), one layer, "
               f"{args.steps} steps, {n_threads} threads")
+    try:    # this arm is the CPU oracle alone: the CUDA library must not even be mapped into the process
+        cuda_lib_mapped = any("libhl_b200" in ln for ln in open("/proc/self/maps"))
+    except OSError:
+        cuda_lib_mapped = None
+    config = workload_config(cfg, args.gpus)
+    config["sequences_timed_per_step"] = n_seq   # the CPU arm times a bounded sample of the 64 sequences per step
+    config["sample"] = sample
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, args.gpus),
+        "config": config,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": n_threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cuda_library_mapped": cuda_lib_mapped,
     }
     print(json.dumps(line), file=result_out, flush=True)
 
@@ -186,7 +199,9 @@ def workload_config(cfg, n_gpus):
     return {"workload": "config 4: batched decode attention, Llama-3-8B shape, one layer",
             "n_head": cfg.n_head, "n_head_kv": cfg.n_head_kv, "head_dim": cfg.head_dim,
             "sequences_per_gpu": cfg.batch, "ctx_range": list(cfg.ctx_range), "kv": "paged fp16",
-            "block_tokens": cfg.block_tokens, "sharding": f"batch x{n_gpus} (own sequences per GPU, no collective)",
+            "block_tokens": cfg.block_tokens,
+            "sharding": f"one seeded set of {cfg.batch * n_gpus} sequences dealt to {n_gpus} GPU(s) greedy longest-first "
+                        "(equal KV bytes per GPU), no collective",
             "l2": "KV working set ~1.1 GB per GPU >> 126 MB L2 (no flush needed)"}
 
 
@@ -200,12 +215,46 @@ def timed_loop(torch, fn, steps):
     return e0.elapsed_time(e1)  # ms
 
 
-def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
-    """Prefill TFLOP/s on the prefill configurations (one layer each), device-resident inputs."""
+# DRAM bytes per launch of the prefill kernels from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum; the
+# summaries under profiles/ give the commands).  None: not captured for that configuration.
+PREFILL_NCU_TRAFFIC = {3: 170.1e6 + 43.7e6}
+
+
+def median_ms(torch, fn, n):
+    """Median of n single-call device timings (CUDA events on the current stream)."""
+    return statistics.median(timed_loop(torch, fn, 1) for _ in range(n))
+
+
+def cpu_prefill_rows(cfg, theta, q, k, v, qw, kw, n_rows, n_threads):
+    """The CPU oracle on a seeded sample of (token, head) rows of one prefill: returns (seconds for the rows,
+    seconds to norm / rotate / append all K and V, rows, their outputs).  Positions are uniform over the prompt, so
+    the mean row attends about half the prompt and the measured rate extrapolates to the whole causal problem."""
+    import oracle
+
+    S = q.shape[0]
+    g = np.random.Generator(np.random.PCG64([cfg.seed, 4242]))
+    rows = np.stack([g.integers(0, S, n_rows), g.integers(0, cfg.n_head, n_rows)], axis=1).astype(np.int32)
+    cache = oracle.SeqCache(S, cfg.n_head_kv, cfg.head_dim)
+    t0 = time.perf_counter()
+    oracle.attn_forward(q, k, v, cache, theta=theta, rope_mode=oracle.ROPE_SPLIT_HALF, q_norm_w=qw, k_norm_w=kw,
+                        eps=cfg.rms_eps, rows=rows[:1], n_threads=n_threads)
+    t_append = time.perf_counter() - t0
+    cache.cur_len = 0
+    t0 = time.perf_counter()
+    out = oracle.attn_forward(q, k, v, cache, theta=theta, rope_mode=oracle.ROPE_SPLIT_HALF, q_norm_w=qw, k_norm_w=kw,
+                              eps=cfg.rms_eps, rows=rows, n_threads=n_threads)
+    return max(time.perf_counter() - t0 - t_append, 1e-9), t_append, rows, out
+
+
+def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5), cpu=True):
+    """Prefill TFLOP/s on the prefill configurations (one layer each): device-resident inputs (the kernel's
+    roofline), end to end through hl_b200_prefill_host (pinned float32 host Q/K/V in, host output back, every call),
+    and the CPU oracle on a row sample of the same problem beside it."""
     import hippo_leap_b200 as hl
     from hippo_leap_b200 import synth
 
     res = {}
+    n_threads = os.cpu_count() or 1
     for ci in configs:
         cfg = synth.CONFIGS[ci]
         S = cfg.prefill
@@ -222,31 +271,142 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5)):
         nb = (S + bt - 1) // bt
         kv = ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, nb)
         table = torch.randperm(nb, generator=gen, device=device).to(torch.int32)
-        q = torch.randn((S, cfg.n_head, cfg.head_dim), generator=gen, device=device)
-        k = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
-        v = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        q32 = torch.randn((S, cfg.n_head, cfg.head_dim), generator=gen, device=device)
+        k32 = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        v32 = torch.randn((S, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
         if cfg.bf16_range:    # values a bf16 model would produce, still handed over as float32
-            q, k, v = (x.bfloat16().float() for x in (q, k, v))
+            q32, k32, v32 = (x.bfloat16().float() for x in (q32, k32, v32))
         if cfg.fp16_inputs:   # activations arrive as fp16
-            q, k, v = (x.half() for x in (q, k, v))
+            q, k, v = (x.half() for x in (q32, k32, v32))
+            q32, k32, v32 = (x.float() for x in (q, k, v))   # the same values widened, for the host-buffer and CPU legs
+        else:
+            q, k, v = q32, k32, v32
         out = torch.empty((S, cfg.n_head, cfg.head_dim), dtype=torch.float16, device=device)
         ctx.kv_append_seq(kv, 0, shape, k, v, 0, table)
-        n = 2 if quick else 5
-        for _ in range(2):
+        n = 3 if quick else 7
+        for _ in range(3):
             ctx.attn_prefill(kv, 0, shape, q, 0, table, out)
-        ms = timed_loop(torch, lambda: ctx.attn_prefill(kv, 0, shape, q, 0, table, out), n) / n
-        ms_app = timed_loop(torch, lambda: ctx.kv_append_seq(kv, 0, shape, k, v, 0, table), n) / n
+        sampler = ClockSampler(device.index or 0)
+        sampler.start()
+        ms = median_ms(torch, lambda: ctx.attn_prefill(kv, 0, shape, q, 0, table, out), n)
+        clocks = sampler.stop()
+        ms_app = median_ms(torch, lambda: ctx.kv_append_seq(kv, 0, shape, k, v, 0, table), n)
         fl = synth.prefill_flops(cfg.n_head, cfg.head_dim, S)
         tf = fl / (ms * 1e-3) / 1e12
-        res[f"config{ci}_prefill"] = {
+        entry = {
             "workload": f"{cfg.name}: causal prefill of {S} tokens, one layer, "
                         f"{'fp16' if cfg.fp16_inputs else 'float32'} Q/K/V in, fp16 out", "ms_attn": ms, "ms_kv_append": ms_app,
             "tflops": tf, "frac_of_tensor_peak": tf / peaks["tflops"], "peak_tflops": peaks["tflops"],
-            "peak_src": peaks["src"], "flops": fl}
-        kv.destroy()
+            "frac_of_sustained_tensor_peak": tf / peaks["tflops_sustained"], "peak_tflops_sustained": peaks["tflops_sustained"],
+            "peak_src": peaks["src"], "flops": fl, "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["tflops"], "traffic": PREFILL_NCU_TRAFFIC.get(ci)}}
         del q, k, v, out
+        # end to end: page-locked float32 host buffers in and out through the host-buffer entry point, every call
+        if not quick:
+            q_h, k_h, v_h = (x.cpu().pin_memory() for x in (q32, k32, v32))
+            out_h = torch.empty_like(q_h).pin_memory()
+            for _ in range(2):
+                ctx.prefill_host(kv, 0, shape, q_h, k_h, v_h, 0, table, out_h)
+            walls = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                ctx.prefill_host(kv, 0, shape, q_h, k_h, v_h, 0, table, out_h)   # synchronises before it returns
+                walls.append(time.perf_counter() - t0)
+            w = statistics.median(walls)
+            entry["e2e"] = {"value": fl / w / 1e12, "unit": "TFLOP/s", "ms": w * 1e3, "tok_per_s": S / w,
+                            "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 4,
+                            "d2h_bytes_per_step": out_h.numel() * 4,
+                            "call": "hl_b200_prefill_host (float32 host Q/K/V in, KV append + attention, float32 host out)"}
+            if cpu:
+                n_rows = {2: 4096, 3: 1024, 5: 256}.get(ci, 256)
+                qn, kn, vn = (x.numpy() for x in (q_h, k_h, v_h))
+                wn = (None if qw is None else qw.cpu().numpy(), None if kw is None else kw.cpu().numpy())
+                t_rows, t_append, rows, want = cpu_prefill_rows(cfg, cfg.theta(), qn, kn, vn, wn[0], wn[1], n_rows,
+                                                                n_threads)
+                pairs = float((rows[:, 0].astype(np.int64) + 1).sum())
+                row_flops = 4.0 * cfg.head_dim * pairs
+                full_s = t_append + fl / (row_flops / t_rows)
+                entry["cpu_baseline"] = {
+                    "value": row_flops / t_rows / 1e12, "unit": "TFLOP/s", "cores": n_threads, "kind": "port",
+                    "rows_per_s": n_rows / t_rows,
+                    "sample": f"{n_rows} seeded (token, head) rows of the same {S}-token problem (positions uniform over the "
+                              f"prompt, {int(pairs)} query-key pairs) in {t_rows:.2f} s on {n_threads} threads, after "
+                              f"{t_append:.2f} s of norm / RoPE / append of all K, V",
+                    "extrapolated_full_problem_s": full_s,
+                    "extrapolation": "measured flop rate of the sampled rows applied to the whole causal problem "
+                                     "(an estimate: the full CPU run was not made)"}
+                # the rows double as a parity check of the benchmarked call
+                got = out_h[torch.from_numpy(rows[:, 0]).long(), torch.from_numpy(rows[:, 1]).long()].numpy()
+                entry["max_abs_vs_oracle_rows"] = float(np.abs(got - want).max())
+            del q_h, k_h, v_h, out_h
+        res[f"config{ci}_prefill"] = entry
+        kv.destroy()
+        del q32, k32, v32
         torch.cuda.empty_cache()
     return res
+
+
+def extra_config1_full(ctx, torch, device):
+    """Configuration 1 in full, driven like the reference's integration test (tests/integration_inference.nim:34-46):
+    a 128-token causal prefill, then 32 decode steps, one attention layer (32 / 4 heads of 64, theta 1e4), float32
+    ~N(0,1) from seed 0 -- on the GPU through the host-buffer entry points (host in, host out, one synchronisation per
+    call) and on the CPU oracle, single-threaded (the reference's tensor ops are) and with all host threads."""
+    import hippo_leap_b200 as hl
+    import oracle
+    from hippo_leap_b200 import synth
+
+    cfg = synth.CONFIGS[1]
+    S, T = cfg.prefill, cfg.decode_steps
+    q, k, v = synth.gen_qkv(cfg, S + T)
+    theta = oracle.theta_table(cfg.head_dim, cfg.rope_base)
+    ctx.set_rope(theta)
+    shape = hl.AttnShape(cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
+    bt = 16
+    nb = (S + T + bt - 1) // bt
+    kv = ctx.kv_create(1, cfg.n_head_kv, cfg.head_dim, bt, nb)
+    table = torch.arange(nb, dtype=torch.int32, device=device)
+    tq, tk, tv = (torch.from_numpy(x).pin_memory() for x in (q, k, v))
+    out = torch.empty_like(tq).pin_memory()
+    ctx_len_steps = [torch.tensor([S + t + 1], dtype=torch.int32, device=device) for t in range(T)]
+
+    def gpu_run():
+        ctx.prefill_host(kv, 0, shape, tq[:S], tk[:S], tv[:S], 0, table, out[:S])
+        for t in range(T):
+            p = S + t
+            ctx.decode_step_host(kv, 0, shape, tq[p:p + 1], tk[p:p + 1], tv[p:p + 1], ctx_len_steps[t], p + 1,
+                                 table.view(1, -1), out[p:p + 1])
+
+    for _ in range(2):
+        gpu_run()
+    walls = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        gpu_run()
+        walls.append(time.perf_counter() - t0)
+    gpu_s = statistics.median(walls)
+
+    def cpu_run(n_threads):
+        cache = oracle.SeqCache(S + T, cfg.n_head_kv, cfg.head_dim)
+        t0 = time.perf_counter()
+        outs = [oracle.attn_forward(q[:S], k[:S], v[:S], cache, theta=theta, rope_mode=oracle.ROPE_SPLIT_HALF,
+                                    n_threads=n_threads)]
+        for t in range(S, S + T):
+            outs.append(oracle.attn_forward(q[t:t + 1], k[t:t + 1], v[t:t + 1], cache, theta=theta,
+                                            rope_mode=oracle.ROPE_SPLIT_HALF, n_threads=n_threads))
+        return time.perf_counter() - t0, np.concatenate(outs)
+
+    cpu1_s, want = cpu_run(1)
+    n_threads = os.cpu_count() or 1
+    cpun_s, _ = cpu_run(n_threads)
+    kv.destroy()
+    return {"workload": "config 1 in full: TinyLlama-1.1B single-layer attention, 128-token causal prefill + 32 decode steps, "
+                        "float32 host buffers in and out of every call",
+            "gpu_ms": gpu_s * 1e3, "gpu_tok_per_s": (S + T) / gpu_s, "gpu_calls": 1 + T,
+            "cpu_baseline": {"value": (S + T) / cpu1_s, "unit": "tok/s", "cores": 1, "kind": "port",
+                             "sample": f"the whole configuration, {cpu1_s * 1e3:.1f} ms", "ms": cpu1_s * 1e3,
+                             "all_threads": {"cores": n_threads, "ms": cpun_s * 1e3, "tok_per_s": (S + T) / cpun_s}},
+            "max_abs_vs_oracle": float(np.abs(out.numpy() - want).max())}
 
 
 def extra_linear(ctx, torch, device, peaks):
@@ -488,6 +648,88 @@ def extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks):
             "scaling": "strong"}
 
 
+def extra_head_sharded_decode(ctx, torch, dist, device, rank, world, peaks):
+    """Configuration 4 with KV heads split across ranks: every rank holds its Hkv/N heads of ALL 64 sequences' pages,
+    runs the decode step on its n_head/N query heads, and the head-major rows are gathered -- once with one NCCL
+    all-gather after the kernels, once by the kernels' own stores to every peer (symmetric memory).  Strong scaling:
+    the 64 sequences are fixed, each rank streams 1/N of the KV bytes."""
+    import hippo_leap_b200 as hl
+    from hippo_leap_b200 import sharding, synth
+
+    cfg = synth.CONFIGS[4]
+    sh = sharding.head_shard(rank, world, cfg.n_head, cfg.n_head_kv)
+    ctx_lens = synth.gen_ctx_lens(cfg)                       # the same 64 sequences and page tables on every rank
+    tables, num_blocks = synth.gen_block_tables(ctx_lens, cfg.block_tokens, cfg.seed)
+    shape = hl.AttnShape(sh.n_head, sh.n_head_kv, cfg.head_dim, cfg.head_dim, hl.HL_ROPE_SPLIT_HALF, cfg.rms_eps)
+    ctx.set_rope(cfg.theta())
+    kv = ctx.kv_create(1, sh.n_head_kv, cfg.head_dim, cfg.block_tokens, num_blocks)
+    ttab = torch.from_numpy(tables).to(device)
+    tctx = torch.from_numpy(ctx_lens).to(device)
+    B = len(ctx_lens)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4000)                                     # the SAME full-width tensors on every rank, sliced by head
+    check_seqs = [int(i) for i in np.argsort(ctx_lens)[:2]]  # the two shortest: checked against the CPU oracle below
+    kept = {}
+    for i, c in enumerate(ctx_lens):
+        k_all = torch.randn((int(c), cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        v_all = torch.randn((int(c), cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+        if rank == 0 and i in check_seqs:
+            kept[i] = (k_all.cpu().numpy(), v_all.cpu().numpy())
+        nb = (int(c) + cfg.block_tokens - 1) // cfg.block_tokens
+        ctx.kv_append_seq(kv, 0, shape, k_all[:, sh.kv_lo:sh.kv_hi], v_all[:, sh.kv_lo:sh.kv_hi], 0,
+                          ttab[i, :nb].contiguous())
+    q_full = torch.randn((B, cfg.n_head, cfg.head_dim), generator=gen, device=device)
+    kn_full = torch.randn((B, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+    vn_full = torch.randn((B, cfg.n_head_kv, cfg.head_dim), generator=gen, device=device)
+    q, kn, vn = q_full[:, sh.q_lo:sh.q_hi], kn_full[:, sh.kv_lo:sh.kv_hi], vn_full[:, sh.kv_lo:sh.kv_hi]
+    max_ctx = int(ctx_lens.max())
+    plain = sharding.HeadShardedDecode(ctx, kv, shape, B, device, world)
+    fused = sharding.FusedHeadShardedDecode(ctx, kv, shape, B, cfg.n_head, device)
+    results = {}
+    n = 50
+    for name, runner in (("fused_in_kernel", fused), ("nccl_allgather_after", plain)):
+        for _ in range(5):
+            runner.run(q, kn, vn, tctx, max_ctx, ttab)
+        vals = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            vals.append(sharding.max_over_ranks(timed_loop(torch, lambda: runner.run(q, kn, vn, tctx, max_ctx, ttab), n) / n,
+                                                device))
+        results[name] = statistics.median(vals)
+    a_ = fused.run(q, kn, vn, tctx, max_ctx, ttab).clone()
+    b_ = plain.run(q, kn, vn, tctx, max_ctx, ttab).clone()
+    torch.cuda.synchronize()
+    same = bool(torch.equal(a_, b_))
+    # the GATHERED tensor against the CPU oracle's unsharded step, all heads of the two shortest sequences (rank 0)
+    max_abs = None
+    if rank == 0:
+        import oracle
+        theta = cfg.theta()
+        max_abs = 0.0
+        for i, (kk, vv) in kept.items():
+            kk, vv = kk.copy(), vv.copy()
+            kk[-1], vv[-1] = kn_full[i].cpu().numpy(), vn_full[i].cpu().numpy()   # the step's own new token
+            sc = oracle.SeqCache(kk.shape[0], cfg.n_head_kv, cfg.head_dim)
+            if kk.shape[0] > 1:
+                oracle.attn_forward(np.zeros((kk.shape[0] - 1, cfg.n_head, cfg.head_dim), np.float32), kk[:-1], vv[:-1], sc,
+                                    theta=theta, rope_mode=oracle.ROPE_SPLIT_HALF, rows=[[0, 0]])
+            want = oracle.attn_forward(q_full[i:i + 1].cpu().numpy(), kk[-1:], vv[-1:], sc, theta=theta,
+                                       rope_mode=oracle.ROPE_SPLIT_HALF)[0]
+            max_abs = max(max_abs, float(np.abs(a_[:, i].cpu().numpy() - want).max()))
+    ms = min(results.values())
+    alg = synth.decode_bytes(ctx_lens, cfg.n_head, cfg.n_head_kv, cfg.head_dim)
+    kv.destroy()
+    return {"workload": f"config 4, KV heads {sh.n_head_kv}/GPU: 64 sequences, one decode step (append + split-KV attention + "
+                        "gather of head outputs to every GPU), float32 rows",
+            "ms_nccl_allgather_after": results["nccl_allgather_after"], "ms_fused_in_kernel": results["fused_in_kernel"],
+            "fused_equals_allgather": same, "max_abs_vs_oracle_two_sequences": max_abs, "ms": ms,
+            "tok_per_s": B / (ms * 1e-3),
+            "aggregate_kv_gbs": alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak_per_gpu": alg / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "gathered_bytes_per_gpu": int(B * cfg.n_head * cfg.head_dim * 4), "scaling": "strong"}
+
+
 def _protect_stdout():
     """Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
     there.  Point fd 1 at stderr for the run and keep the real stdout for the result line."""
@@ -512,7 +754,7 @@ def main():
     ap.add_argument("--dense-only", action="store_true", help="measure only the dense Llama-3.2-1B model")
     ap.add_argument("--pipeline-only", action="store_true", help="measure only the config 2 backend pipeline")
     ap.add_argument("--head-sharded-only", action="store_true",
-                    help="measure only the head-sharded config 5 prefill + all-gather at N GPUs")
+                    help="measure only the head-sharded config 5 prefill and config 4 decode (+ gather) at N GPUs")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="CFG",
                     help="measure only the prefill kernel of configuration 2, 3 or 5 (small profiling target)")
     args = ap.parse_args()
@@ -529,7 +771,7 @@ def main():
     import torch.distributed as dist
 
     import hippo_leap_b200 as hl
-    from hippo_leap_b200 import synth
+    from hippo_leap_b200 import sharding, synth
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback (use --impl reference for the CPU arm)")
@@ -554,7 +796,8 @@ def main():
         ctx.close()
         return
     if args.head_sharded_only:
-        res = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks)
+        res = {"config5_head_sharded_prefill": extra_head_sharded_prefill(ctx, torch, dist, device, rank, world, peaks),
+               "config4_head_sharded_decode": extra_head_sharded_decode(ctx, torch, dist, device, rank, world, peaks)}
         if rank == 0:
             print(json.dumps(res), file=result_out, flush=True)
         ctx.close()
@@ -566,8 +809,20 @@ def main():
         print(json.dumps(res), file=result_out, flush=True)
         ctx.close()
         return
-    w = setup_decode(ctx, cfg, rank, device)
-    B = len(w["ctx_lens"])
+    w = setup_decode(ctx, cfg, rank, world, device)
+    B = len(w["ctx_lens"])            # this rank's sequences
+    B_total = w["total_sequences"]    # all ranks': cfg.batch * world
+    REPEATS = 5                       # every figure below is the median of this many K-step regions
+
+    def region(fn, steps):
+        """One timed region: barrier + synchronize on both sides, K steps, CUDA events, max over ranks."""
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = timed_loop(torch, fn, steps)   # ends with a synchronize
+        if world > 1:
+            dist.barrier()
+        return sharding.max_over_ranks(ms, device)
 
     def step():
         ctx.kv_append_batch(w["kv"], 0, w["shape"], w["kn"], w["vn"], w["tctx"], w["ttab"])
@@ -575,32 +830,41 @@ def main():
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     l0 = ctx.launch_count()
-    ms_local = timed_loop(torch, step, args.steps)
-    launches = ctx.launch_count() - l0
-    t = torch.tensor([ms_local], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.barrier()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    value = world * B * args.steps / (ms_total * 1e-3)
+    region_ms = [region(step, args.steps) for _ in range(REPEATS)]
+    launches = (ctx.launch_count() - l0) // REPEATS
+    ms_total = statistics.median(region_ms)
+    value = B_total * args.steps / (ms_total * 1e-3)
 
-    # roofline of the dominant kernel pair (split-KV decode + combine), timed alone
-    for _ in range(3):
+    # roofline of the dominant kernel pair (split-KV decode + combine), timed alone on every rank; the line reports
+    # the SLOWEST rank's launch (the one that bounds the step) and lists all ranks
+    def attn_only():
         ctx.attn_decode(w["kv"], 0, w["shape"], w["q"], w["tctx"], w["max_ctx"], w["ttab"], w["out"])
-    ms_attn = timed_loop(torch, lambda: ctx.attn_decode(w["kv"], 0, w["shape"], w["q"], w["tctx"], w["max_ctx"],
-                                                        w["ttab"], w["out"]), args.steps) / args.steps
+
+    for _ in range(3):
+        attn_only()
+    ms_attn = statistics.median(timed_loop(torch, attn_only, args.steps) / args.steps for _ in range(REPEATS))
     alg_bytes = synth.decode_bytes(w["ctx_lens"], cfg.n_head, cfg.n_head_kv, cfg.head_dim)
-    achieved = alg_bytes / (ms_attn * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel<128,...> + attn_combine_kernel<128>",
+    mine = torch.tensor([alg_bytes, ms_attn, float(B)], device=device, dtype=torch.float64)
+    per = [mine.clone() for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per, mine)
+    per_rank = [{"rank": r, "sequences": int(x[2].item()), "algorithmic_bytes_per_launch": float(x[0].item()),
+                 "ms_per_launch": float(x[1].item()), "gbs": float(x[0].item() / (x[1].item() * 1e-3) / 1e9)}
+                for r, x in enumerate(per)]
+    slow = max(per_rank, key=lambda e: e["ms_per_launch"])
+    achieved = slow["gbs"]
+    # ncu (profiles/attn_decode_config4.md): 1006.9 MB of DRAM traffic per launch for the 997.4 MB one-GPU workload,
+    # i.e. 1.0096 x the algorithmic bytes; a rank's share of a larger set scales with its algorithmic bytes
+    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel<128,4,3> + attn_combine_kernel<128>",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "peak_src": peaks["src"], "traffic": None, "algorithmic_bytes_per_launch": alg_bytes,
-                "ms_per_launch": ms_attn}
+                "peak_src": peaks["src"], "traffic": NCU_DECODE_TRAFFIC_RATIO * slow["algorithmic_bytes_per_launch"],
+                "traffic_src": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the one-GPU workload, scaled by "
+                               "algorithmic bytes",
+                "algorithmic_bytes_per_launch": slow["algorithmic_bytes_per_launch"],
+                "ms_per_launch": slow["ms_per_launch"], "rank": slow["rank"], "per_rank": per_rank}
 
     # end to end through the host-buffer C ABI call: pinned host inputs, host result, every step
     q_h, k_h, v_h = (x.cpu().pin_memory() for x in (w["q"], w["kn"], w["vn"]))
@@ -611,16 +875,15 @@ def main():
 
     for _ in range(3):
         step_host()
+    e2e_ms = [region(step_host, args.steps) for _ in range(REPEATS)]
+    ms_e2e = statistics.median(e2e_ms)
+    e2e_value = B_total * args.steps / (ms_e2e * 1e-3)
+    io = torch.tensor([q_h.numel() * 4 + k_h.numel() * 4 + v_h.numel() * 4, out_h.numel() * 4], device=device,
+                      dtype=torch.float64)
     if world > 1:
-        dist.barrier()
-    ms_e2e = timed_loop(torch, step_host, args.steps)
-    t2 = torch.tensor([ms_e2e], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_value = world * B * args.steps / (float(t2.item()) * 1e-3)
-    h2d = q_h.numel() * 4 + k_h.numel() * 4 + v_h.numel() * 4
-    d2h = out_h.numel() * 4
-    clocks = sampler.stop()  # sampled across the three timed loops above (device, kernel-only, end-to-end)
+        dist.all_reduce(io)               # whole-job bytes per step: the sum over ranks
+    h2d, d2h = int(io[0].item()), int(io[1].item())
+    clocks = sampler.stop()  # sampled across the timed loops above (device, kernel-only, end-to-end)
     code, detail = ctx.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) after the timed region")
@@ -628,13 +891,15 @@ def main():
     extra = {}
     if not args.no_extras:
         if world == 1:
-            extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False))
+            extra.update(extras_single_gpu(ctx, torch, device, peaks, quick=False, cpu=not args.no_cpu))
+            extra["config1_full"] = extra_config1_full(ctx, torch, device)
             extra["config2_backend_pipeline"] = extra_config2_pipeline(torch, local_rank)
             extra["linear_f16"] = extra_linear(ctx, torch, device, peaks)
             extra["dense_llama32_1b"] = extra_dense_model(torch, local_rank)
         if cfg.n_head_kv % world == 0:
             extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
                                                                                peaks)
+            extra["config4_head_sharded_decode"] = extra_head_sharded_decode(ctx, torch, dist, device, rank, world, peaks)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -649,12 +914,14 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "repeats": REPEATS,
+            "ms_per_step_each_repeat": [m / args.steps for m in region_ms], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV, f32 accumulate", "data": "synthetic",
             "config": workload_config(cfg, world),
             "hbm_gbs": achieved, "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": float(t2.item()) / args.steps},
+                    "ms_per_step": ms_e2e / args.steps, "ms_per_step_each_repeat": [m / args.steps for m in e2e_ms],
+                    "call": "hl_b200_decode_step_host (pinned float32 host q / k / v in, host out, every step)"},
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
         }
         print(json.dumps(line), file=result_out, flush=True)

@@ -113,6 +113,9 @@ __global__ void __launch_bounds__(192, 2)
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
+    // Read before griddepcontrol.wait on purpose: an earlier grid may still be running and may yet set the status
+    // word, so this only catches failures that are already visible.  Missing a late one is harmless -- the flag only
+    // shortens this CTA's own bounded waits -- and the host still reads the status word after the stream drains.
     *abort_flag = (g.status != nullptr && *g.status != 0) ? 1 : 0;
     mbar_fence_init();
   }

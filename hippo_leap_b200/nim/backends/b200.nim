@@ -23,8 +23,8 @@ when not defined(cpp):
   {.error: "the b200 backend requires Nim's C++ backend. Build with `nim cpp`.".}
 
 import
-  std/tables,
-  ../[model, tensor, backend_types, quant]
+  std/[tables, sequtils],
+  ../[model, tensor, backend_types]
 
 const hlLib = "libhl_b200.so"
 
@@ -91,7 +91,10 @@ proc hl_b200_kv_layer(kv: pointer, layer: int32, kPool, vPool: ptr pointer,
                       bytesEach: ptr csize_t): int32 {.importc, cdecl, dynlib: hlLib.}
 
 var
-  shimCache: HlKvCache          # one model, one cache per process, like naive.nim:235-239
+  # One library-side cache per KvCache handed out by initKvCache, keyed by the device pointer of its layer-0 K pool
+  # (KvCache has no spare field for a handle).  Each KvCache owns its own device pools, as in the reference
+  # (initGpuKvCache, naive.nim:3552-3567); all of them are freed by unloadModelBackend.
+  shimCaches: Table[pointer, HlKvCache]
   shimHp: HlHParams
 
 proc check(rc: int32) =
@@ -107,13 +110,17 @@ proc toHl(hp: HParams): HlHParams =
             ropeFreqBase: hp.ropeFreqBase, rmsEps: hp.rmsEps,
             ropeMode: HlRopeSplitHalf, llama3Scaling: 0)
 
-proc syncIn(cache: KvCache) =
-  ## Callers reset cache.curLen themselves (inference.nim:58); honour it.
-  shimCache.curLen = cache.curLen.int32
+proc syncIn(cache: KvCache): ptr HlKvCache =
+  ## The library-side cache behind `cache`, with the caller's curLen: callers reset cache.curLen themselves
+  ## (inference.nim:58); honour it.
+  if cache.gpuCache.k.len == 0 or cache.gpuCache.k[0].devicePtr notin shimCaches:
+    raise newException(ValueError, "KvCache was not created by this backend's initKvCache")
+  result = addr shimCaches[cache.gpuCache.k[0].devicePtr]
+  result.curLen = cache.curLen.int32
 
-proc syncOut(cache: var KvCache) =
-  cache.curLen = shimCache.curLen.int
-  cache.gpuCache.curLen = shimCache.curLen.int     # naive.nim:4586-4587
+proc syncOut(cache: var KvCache, shim: ptr HlKvCache) =
+  cache.curLen = shim.curLen.int
+  cache.gpuCache.curLen = shim.curLen.int          # naive.nim:4586-4587
 
 proc toDense(hp: HParams): HlDenseHParams =
   HlDenseHParams(nVocab: hp.nVocab.int32, nEmb: hp.nEmb.int32, nLayer: hp.nLayer.int32, nFfn: hp.nFfn.int32,
@@ -124,6 +131,7 @@ proc toDense(hp: HParams): HlDenseHParams =
 var shimDenseHp: HlDenseHParams
 
 proc initKvCache*(hp: HParams, maxLen: int): KvCache =
+  var shimCache: HlKvCache
   when defined(b200Standin):
     shimHp = toHl(hp)
     check hl_backend_init_kv_cache(0, addr shimHp, maxLen.int32, addr shimCache)
@@ -151,16 +159,43 @@ proc initKvCache*(hp: HParams, maxLen: int): KvCache =
                                          sizeBytes: bytes.int)
     result.gpuCache.v[layer] = GpuTensor(devicePtr: vp, shape: @[numBlocks, hp.nHeadKv, blockTokens, hp.headDim],
                                          sizeBytes: bytes.int)
+  shimCaches[result.gpuCache.k[0].devicePtr] = shimCache
+
+proc floatToHalfRne(f: float32): uint16 =
+  ## float32 -> fp16 bit pattern, round to nearest even, subnormals kept: the rounding of the CUDA kernels
+  ## (__float2half_rn) and of the tested Python mirror (numpy's astype(float16)).  quant.floatToHalf
+  ## (quant.nim:98-107) truncates the mantissa and flushes subnormals to zero, which would give this build other
+  ## weights than the ones the parity tests ran on.  Values that are exact in fp16 (an F16 GGUF) convert exactly.
+  let bits = cast[uint32](f)
+  let sign = uint16((bits shr 16) and 0x8000'u32)
+  let a = bits and 0x7FFFFFFF'u32
+  if a > 0x7F800000'u32: return sign or 0x7E00'u16            # NaN
+  if a >= 0x47800000'u32: return sign or 0x7C00'u16           # >= 65536 (and inf): infinity
+  if a >= 0x38800000'u32:                                     # normal half: |f| >= 2^-14
+    var h = (((a shr 23) - 112'u32) shl 10) or ((a shr 13) and 0x3FF'u32)
+    let rem = a and 0x1FFF'u32
+    if rem > 0x1000'u32 or (rem == 0x1000'u32 and (h and 1'u32) == 1'u32): inc h   # a carry rolls into the exponent
+    return sign or uint16(h)
+  if a < 0x33000000'u32: return sign                          # below 2^-25: rounds to zero
+  # subnormal half: units of 2^-24.  |f| = m * 2^(e - 150) with the 24-bit significand m, so the result is m >> (126 - e)
+  let e = a shr 23
+  let m = (a and 0x7FFFFF'u32) or 0x800000'u32
+  let shift = 126'u32 - e                                     # 14 .. 24
+  var r = m shr shift
+  let rem = m and ((1'u32 shl shift) - 1'u32)
+  let halfway = 1'u32 shl (shift - 1'u32)
+  if rem > halfway or (rem == halfway and (r and 1'u32) == 1'u32): inc r
+  return sign or uint16(r)
 
 proc halfRows(m: var Model, names: openArray[string]): seq[uint16] =
-  ## The named float32 tensors, one after the other, as fp16 bit patterns.  F16 GGUF values convert exactly;
-  ## other source types are truncated by quant.floatToHalf (quant.nim:98-107).
+  ## The named float32 tensors, one after the other, as fp16 bit patterns, rounded to nearest even.  F16 GGUF
+  ## values convert exactly.
   for name in names:
     let t = m.getTensor(name)
     let base = result.len
     result.setLen(base + t.data.len)
     for i, v in t.data:
-      result[base + i] = floatToHalf(v)
+      result[base + i] = floatToHalfRne(v)
 
 proc floatRows(m: var Model, names: openArray[string]): seq[float32] =
   for name in names:
@@ -210,46 +245,50 @@ proc loadModelBackend*(m: var Model, hp: HParams) =
     check hl_dense_load_model(0, addr shimDenseHp, addr w)   # the library copies everything to the device
 
 proc unloadModelBackend*() =
+  for key in toSeq(shimCaches.keys):
+    when defined(b200Standin):
+      discard hl_backend_free_kv_cache(addr shimCaches[key])
+    else:
+      discard hl_dense_free_kv_cache(addr shimCaches[key])
+  shimCaches.clear()
   when defined(b200Standin):
-    discard hl_backend_free_kv_cache(addr shimCache)
     check hl_backend_unload_model()
   else:
-    discard hl_dense_free_kv_cache(addr shimCache)
     check hl_dense_unload_model()
 
 proc forwardPrefill*(m: var Model, tokens: seq[int32], cache: var KvCache): Tensor =
   if tokens.len == 0:
     raise newException(ValueError, "prefill requires at least one token")
   result = newTensor(@[1, m.hparams.nVocab])      # last position only, like megakernel.nim:2498
-  syncIn(cache)
+  let shim = syncIn(cache)
   when defined(b200Standin):
-    check hl_backend_forward_prefill(unsafeAddr tokens[0], tokens.len.int32, addr shimCache, addr result.data[0])
+    check hl_backend_forward_prefill(unsafeAddr tokens[0], tokens.len.int32, shim, addr result.data[0])
   else:
-    check hl_dense_forward_prefill(unsafeAddr tokens[0], tokens.len.int32, addr shimCache, addr result.data[0])
-  syncOut(cache)
+    check hl_dense_forward_prefill(unsafeAddr tokens[0], tokens.len.int32, shim, addr result.data[0])
+  syncOut(cache, shim)
 
 proc forwardDecode*(m: var Model, token: int32, cache: var KvCache): Tensor =
   result = newTensor(@[1, m.hparams.nVocab])
-  syncIn(cache)
+  let shim = syncIn(cache)
   when defined(b200Standin):
-    check hl_backend_forward_decode(token, addr shimCache, addr result.data[0])
+    check hl_backend_forward_decode(token, shim, addr result.data[0])
   else:
-    check hl_dense_forward_decode(token, addr shimCache, addr result.data[0])
-  syncOut(cache)
+    check hl_dense_forward_decode(token, shim, addr result.data[0])
+  syncOut(cache, shim)
 
 proc forwardDecodeToken*(m: var Model, token: int32, cache: var KvCache): int32 =
-  syncIn(cache)
+  let shim = syncIn(cache)
   when defined(b200Standin):
-    check hl_backend_forward_decode_token(token, addr shimCache, addr result)
+    check hl_backend_forward_decode_token(token, shim, addr result)
   else:
-    check hl_dense_forward_decode_token_timed(token, addr shimCache, addr result, nil)
-  syncOut(cache)
+    check hl_dense_forward_decode_token_timed(token, shim, addr result, nil)
+  syncOut(cache, shim)
 
 proc forwardDecodeTokenTimed*(m: var Model, token: int32, cache: var KvCache,
                               gpuMs: var float32): int32 =
-  syncIn(cache)
+  let shim = syncIn(cache)
   when defined(b200Standin):
-    check hl_backend_forward_decode_token_timed(token, addr shimCache, addr result, addr gpuMs)
+    check hl_backend_forward_decode_token_timed(token, shim, addr result, addr gpuMs)
   else:
-    check hl_dense_forward_decode_token_timed(token, addr shimCache, addr result, addr gpuMs)
-  syncOut(cache)
+    check hl_dense_forward_decode_token_timed(token, shim, addr result, addr gpuMs)
+  syncOut(cache, shim)
