@@ -22,6 +22,8 @@
 #pragma once
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "attn_prefill_mma.cuh"
 #include "hl_device.cuh"
 #include "host_common.h"
@@ -63,6 +65,33 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Lean forms for the issuing thread's inner loop.  A shared-memory matrix descriptor only varies in its low word (start
+// address and leading byte offset, both in 16-byte units); the high word (stride byte offset, version, swizzle mode) is
+// a constant of the layout.  Stepping an operand along K is then ONE 32-bit add per MMA: measured, building both
+// descriptors from scratch for every MMA (~25 scalar instructions) made the single issuing thread, not the tensor
+// pipe, the bound -- 85 cycles per 128x128x16 MMA against the 64 the pipe takes when fed.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ void tc_mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
       : "memory");
 }
 #define HL_R32(a, o)                                                                                        \
@@ -227,8 +256,8 @@ struct PrefillTcCfg {
   static constexpr int kRowOff = kVOff + (kStagesV - 1) * kTileBytes;
   static constexpr int kBarOff = kVOff + kStagesV * kTileBytes;
   static constexpr int kNumBars = 2 * kStagesK + 2 * kStagesV + 7;
-  static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 16;
-  static constexpr int kThreads = 384;  // 12 warps: two softmax warpgroups + one warpgroup holding the TMA and MMA warps
+  static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 32;  // + TMEM slot, abort flag, relay counters
+  static constexpr int kThreads = 384;  // 12 warps: two softmax warpgroups + one warpgroup: TMA, MMA, two barrier scouts
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS = 0, kColO = 256;  // S_t at t*128, O_t at 256 + t*HD
 };
@@ -239,6 +268,24 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, int32_t*
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  report(status, HL_ERR_TIMEOUT, where);
+  return false;
+}
+
+// Step counters relayed through shared memory from a scout thread (which waits on the barriers) to the MMA thread.
+__device__ __forceinline__ void relay_publish(uint32_t* flag, uint32_t value) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(flag)), "r"(value) : "memory");
+}
+__device__ __forceinline__ bool relay_wait(uint32_t* flag, uint32_t need, int32_t* status, int32_t where,
+                                           volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(flag);
+  for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {  // a poll is a plain load: far shorter than a try_wait time slice
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    if (v >= need) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   report(status, HL_ERR_TIMEOUT, where);
@@ -276,6 +323,8 @@ __global__ void __launch_bounds__(384, 1)
   uint64_t* q_ready = bars + 2 * SK + 2 * SV + 6;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // Relay counters: what the scout warps have seen complete, as step counts: [0] K/V operands, [1] / [2] P of tile A / B.
+  uint32_t* relay = tmem_slot + 2;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -306,6 +355,7 @@ __global__ void __launch_bounds__(384, 1)
     }
     mbar_init(q_ready, 256);
     *abort_flag = (a.status != nullptr && *a.status != 0) ? 1 : 0;  // an earlier CTA already failed
+    relay[0] = relay[1] = relay[2] = 0u;
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -373,22 +423,27 @@ __global__ void __launch_bounds__(384, 1)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(128, 128, 0);
       constexpr uint32_t idesc_pv = umma_idesc(128, HD, 1);
-      auto issue_qk = [&](int t, int j) {
-        const uint32_t a_base = base + Cfg::kQOff + t * Cfg::kTileBytes;
-        const uint32_t b_base = base + Cfg::kKOff + (j % SK) * Cfg::kTileBytes;
+      constexpr uint32_t kHi = umma_desc_hi(1024);  // every operand here: 8-row groups 1024 bytes apart, 128-byte swizzle
+      const uint32_t q_lo0 = umma_desc_lo(base + Cfg::kQOff, 16);
+      const uint32_t k_lo0 = umma_desc_lo(base + Cfg::kKOff, 16);
+      const uint32_t v_lo0 = umma_desc_lo(base + Cfg::kVOff, Cfg::kHalfBytes);
+      // S_t = Q_t K^T for the K block in stage `stage`
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t a_lo = q_lo0 + t * (Cfg::kTileBytes >> 4), b_lo = k_lo0 + stage * (Cfg::kTileBytes >> 4);
+        const uint32_t d = tmem + Cfg::kColS + t * 128;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * Cfg::kHalfBytes + (ks & 3) * 32;
-          tc_mma_ss(tmem + Cfg::kColS + t * 128, umma_desc(a_base + off, 16, 1024), umma_desc(b_base + off, 16, 1024),
-                    idesc_qk, ks > 0 ? 1u : 0u);
+          const uint32_t off16 = static_cast<uint32_t>(((ks >> 2) * Cfg::kHalfBytes + (ks & 3) * 32) >> 4);  // a constant
+          tc_mma_ss_lo(d, a_lo + off16, b_lo + off16, kHi, idesc_qk, ks > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int j) {
-        const uint32_t b_base = base + Cfg::kVOff + (j % SV) * Cfg::kTileBytes;
+      // O_t (+)= P_t V for the V block in stage `stage`; `first` clears the accumulator
+      auto issue_pv = [&](int t, int stage, bool first) {
+        const uint32_t b_lo = v_lo0 + stage * (Cfg::kTileBytes >> 4);
+        const uint32_t d = tmem + Cfg::kColO + t * HD, p_tmem = tmem + Cfg::kColS + t * 128;
+        tc_mma_ts_lo(d, p_tmem, b_lo, kHi, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          tc_mma_ts(tmem + Cfg::kColO + t * HD, tmem + Cfg::kColS + t * 128 + ks * 8,
-                    umma_desc(b_base + ks * 2048, Cfg::kHalfBytes, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 1; ks < 8; ++ks) tc_mma_ts_lo(d, p_tmem + ks * 8, b_lo + ks * (2048 >> 4), kHi, idesc_pv, 1u);
       };
       tc_wait(q_ready, 0, a.status, 520, abort_flag);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -403,31 +458,57 @@ __global__ void __launch_bounds__(384, 1)
           }
         tc_commit(&k_empty[0]);
       }
+      int sk_next = SK > 1 ? 1 : 0, sv = 0;  // stage of K block j + 1, stage of V block j
       for (int j = 0; j < n_max; ++j) {
         bool next_qk = false;
+        // Nothing in this loop waits on a barrier: for the thread that issues the MMAs a barrier wait is taken in order
+        // behind the MMAs it has queued (~250 cycles measured even when the phase completed long ago; with six of them
+        // per step the tensor pipe idled a third of the time).  The scout warps wait instead and publish step counts in
+        // shared memory, which this thread reads with plain acquire loads.
+        relay_wait(&relay[0], j + 1, a.status, 532, abort_flag);  // V of block j and K of block j + 1 have landed
+#pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= n_blk[t]) continue;
-          tc_wait(&p_full[t], j & 1, a.status, 530 + t, abort_flag);
-          tc_wait(&v_full[j % SV], (j / SV) & 1, a.status, 532, abort_flag);
+          relay_wait(&relay[1 + t], j + 1, a.status, 530 + t, abort_flag);  // P of tile t, block j, is in TMEM
           tc_fence_after();
-          issue_pv(t, j);
+          issue_pv(t, sv, j == 0);
           if (j + 1 < n_blk[t]) {
-            tc_wait(&k_full[(j + 1) % SK], ((j + 1) / SK) & 1, a.status, 533, abort_flag);
-            tc_fence_after();
-            issue_qk(t, j + 1);
+            issue_qk(t, sk_next);
             tc_commit(&s_full[t]);
             next_qk = true;
           } else {
             tc_commit(&o_full[t]);
           }
         }
-        tc_commit(&v_empty[j % SV]);
-        if (next_qk) tc_commit(&k_empty[(j + 1) % SK]);
+        tc_commit(&v_empty[sv]);
+        if (next_qk) tc_commit(&k_empty[sk_next]);
+        sv = sv + 1 == SV ? 0 : sv + 1;
+        sk_next = sk_next + 1 == SK ? 0 : sk_next + 1;
       }
     }
     __syncwarp();
   } else if (warp >= 10) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");  // idle warps of the third warpgroup
+    // ======================= barrier scouts =======================
+    // Warp 10 watches the K/V operand barriers and tile A's P barrier, warp 11 tile B's P barrier, in the order the
+    // MMA warp needs them, and publish how far they got (release stores; the MMA thread's acquire loads pair with them,
+    // so what the barrier ordered before the scout's wait -- TMA writes, the softmax threads' TMEM stores -- is ordered
+    // before the MMA thread's next instruction too).
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (lane == 0) {
+      const int t = warp - 10;
+      for (int j = 0; j < n_max; ++j) {
+        if (t == 0) {
+          tc_wait(&v_full[j % SV], (j / SV) & 1, a.status, 560, abort_flag);
+          if (j + 1 < n_max) tc_wait(&k_full[(j + 1) % SK], ((j + 1) / SK) & 1, a.status, 561, abort_flag);
+          relay_publish(&relay[0], j + 1);
+        }
+        if (j < n_blk[t]) {
+          tc_wait(&p_full[t], j & 1, a.status, 562 + t, abort_flag);
+          relay_publish(&relay[1 + t], j + 1);
+        }
+      }
+    }
+    __syncwarp();
   } else {
     // ======================= softmax warps (tile t, row r) =======================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
@@ -575,7 +656,16 @@ __global__ void __launch_bounds__(384, 1)
 
     float m = -INFINITY, l = 0.f;
     const float c = a.scale_log2;
-    for (int j = 0; j < n_blk[t]; ++j) {
+    // One key block of the online softmax.  `first` (a compile-time tag) is the tile's first block, whose row maximum
+    // must be known before any exponential.  Every later block starts its exponentials at once against the RUNNING
+    // maximum -- which is what they would be taken against anyway unless the row maximum grows by more than 2^8 -- and
+    // computes the block's row maximum next to them (independent instruction streams in one basic block: the max
+    // chain on the ALU, the exponentials on the special-function unit).  With the maximum first, its dependency chain
+    // (~240 cycles, alone on its scheduler) sat in front of every block of the S -> P -> S chain that bounds the loop.
+    // When a row does need a higher maximum (rare after the first blocks), the accumulator is rescaled and the first
+    // half of the block is simply done again: S is still whole in TMEM because no P has been stored yet.
+    auto softmax_block = [&](auto first_tag, int j) {
+      constexpr bool first = decltype(first_tag)::value;
       float s[128];
       tc_wait(&s_full[t], j & 1, a.status, 540 + t, abort_flag);
       tc_fence_after();
@@ -583,15 +673,14 @@ __global__ void __launch_bounds__(384, 1)
       for (int q4 = 0; q4 < 4; ++q4) tc_ld32f(tS + q4 * 32, s + q4 * 32);
       tc_wait_ld();
       const int key0 = j * 128;
-      if (key0 + 127 > a.start_pos + t0 + 128 * t) {  // block touches this tile's diagonal
+      const bool diag = key0 + 127 > a.start_pos + t0 + 128 * t;  // block touches this tile's diagonal
+      if (diag) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (key0 + i > pos) s[i] = -INFINITY;
       }
-      // row maximum: four independent chains of 3-input max (short dependency chains: one warp per
-      // scheduler runs this alone, so instruction-level parallelism is all the latency hiding there is)
-      float mx;
-      {
+      // row maximum: four independent chains of 3-input max
+      auto row_max = [&]() {
         float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
         for (int i = 4; i < 128; i += 8) {
@@ -602,11 +691,35 @@ __global__ void __launch_bounds__(384, 1)
             m4[3] = max3(m4[3], s[i + 6], s[i + 7]);
           }
         }
-        mx = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
-      }
-      if (j == 0) {
-        m = mx;
+        return fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
+      };
+      uint64_t sum2[4];  // four independent packed accumulators
+      uint32_t pk[64];
+      // 64 exponentials against the maximum m: P as fp16 pairs in pk, row sums in sum2
+      auto exp_half = [&](auto half_tag) {
+        constexpr int half_i = decltype(half_tag)::value;
+        const float mc = m * c;
+        const uint64_t c2 = pack_f32x2(c, c), nmc2 = pack_f32x2(-mc, -mc);
+#pragma unroll
+        for (int i = half_i * 64; i < half_i * 64 + 64; i += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(s[i], s[i + 1]), c2, nmc2), x0, x1);
+          const bool poly = HL_TC_POLY_MASK >= 0 && ((i >> 1) & HL_TC_POLY_MASK) == HL_TC_POLY_MASK;  // compile-time
+          const float p0 = poly ? exp2_poly(x0) : fast_exp2(x0);
+          const float p1 = poly ? exp2_poly(x1) : fast_exp2(x1);
+          sum2[(i >> 1) & 3] = add_f32x2(sum2[(i >> 1) & 3], pack_f32x2(p0, p1));
+          pk[i >> 1] = pack_half2(p0, p1);
+        }
+      };
+      using Half0 = std::integral_constant<int, 0>;
+      using Half1 = std::integral_constant<int, 1>;
+      sum2[0] = sum2[1] = sum2[2] = sum2[3] = 0ull;  // bits of +0.0f pairs
+      if constexpr (first) {
+        m = row_max();
+        exp_half(Half0{});
       } else {
+        exp_half(Half0{});  // optimistic: against the running maximum
+        const float mx = row_max();
         const bool need = (mx - m) * c > 8.0f;
         if (__any_sync(0xffffffffu, need)) {
           const float f = need ? fast_exp2((m - mx) * c) : 1.0f;
@@ -622,26 +735,23 @@ __global__ void __launch_bounds__(384, 1)
             tc_st32f(tO + q4 * 32, oreg);
           }
           tc_wait_st();
+          // the first half again, against the raised maximum (the whole warp: the TMEM load is warp-wide; rows that
+          // kept their maximum get the same values as before)
+          tc_ld32f(tS, s);
+          tc_ld32f(tS + 32, s + 32);
+          tc_wait_ld();
+          if (diag) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (key0 + i > pos) s[i] = -INFINITY;
+          }
+          sum2[0] = sum2[1] = sum2[2] = sum2[3] = 0ull;
+          exp_half(Half0{});
         }
       }
-      const float mc = m * c;
-      const uint64_t c2 = pack_f32x2(c, c), nmc2 = pack_f32x2(-mc, -mc);
-      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four independent packed accumulators (bits of +0.0f pairs)
-      uint32_t pk[64];
-#pragma unroll
-      for (int half_i = 0; half_i < 2; ++half_i) {
-#pragma unroll
-        for (int i = half_i * 64; i < half_i * 64 + 64; i += 2) {
-          float x0, x1;
-          unpack_f32x2(fma_f32x2(pack_f32x2(s[i], s[i + 1]), c2, nmc2), x0, x1);
-          const bool poly = HL_TC_POLY_MASK >= 0 && ((i >> 1) & HL_TC_POLY_MASK) == HL_TC_POLY_MASK;  // compile-time
-          const float p0 = poly ? exp2_poly(x0) : fast_exp2(x0);
-          const float p1 = poly ? exp2_poly(x1) : fast_exp2(x1);
-          sum2[(i >> 1) & 3] = add_f32x2(sum2[(i >> 1) & 3], pack_f32x2(p0, p1));
-          pk[i >> 1] = pack_half2(p0, p1);
-        }
-        tc_st32(tS + half_i * 32, pk + half_i * 32);  // first half of P is on its way while the second is computed
-      }
+      tc_st32(tS, pk);  // the first half of P is on its way while the second is computed
+      exp_half(Half1{});
+      tc_st32(tS + 32, pk + 32);
       {
         float a0, a1;
         unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
@@ -650,7 +760,9 @@ __global__ void __launch_bounds__(384, 1)
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
-    }
+    };
+    if (n_blk[t] > 0) softmax_block(std::true_type{}, 0);
+    for (int j = 1; j < n_blk[t]; ++j) softmax_block(std::false_type{}, j);
     // ---- epilogue: O / l -> out ----
     if (n_blk[t] > 0) {
       tc_wait(&o_full[t], 0, a.status, 550 + t, abort_flag);
