@@ -81,12 +81,17 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   // ctx_lens is device data the host cannot see: a value beyond what the grid and the partial slots were sized for
   // (max_ctx_h) is reported and clamped, so the combine pass never reads past this row's slots; a non-positive one
   // (decode always attends at least the new token's own key) is reported and the output row is zeroed.
+  // Launched with programmatic stream serialisation this grid starts while the kernel in front (the KV append of the
+  // same step) is still running.  What that kernel writes -- the cache -- is only touched after griddepcontrol.wait;
+  // the barrier set-up and the query prologue run before it.  Every thread passes a wait before it exits, so that a
+  // grid queued behind this one can rely on everything in front of this one having completed too.
   int ctx = a.ctx_lens[b];
   if (ctx > a.max_chunks * a.chunk_tokens) {
     report(a.status, HL_ERR_BOUNDS, b);
     ctx = a.max_chunks * a.chunk_tokens;
   }
   if (ctx <= 0) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (chunk == 0) {
       report(a.status, HL_ERR_BOUNDS, b);
       for (int idx = threadIdx.x; idx < a.group * HD; idx += blockDim.x)
@@ -95,7 +100,10 @@ __global__ void __launch_bounds__((NW + 1) * 32)
     return;
   }
   const int t_begin = chunk * a.chunk_tokens;
-  if (t_begin >= ctx) return;  // uniform for the CTA
+  if (t_begin >= ctx) {  // uniform for the CTA
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
   const int t_end = min(ctx, t_begin + a.chunk_tokens);
   const int n_iter = (t_end - t_begin + Cfg::kStageTok - 1) / Cfg::kStageTok;
   const int n_chunks_seq = (ctx + a.chunk_tokens - 1) / a.chunk_tokens;
@@ -128,6 +136,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the append in front has written this step's K / V rows
     constexpr int kOpsPerGroup = 2 * Cfg::kHalves;  // K halves + V halves of one 16-row group
     constexpr int kOps = NW * kOpsPerGroup;
     static_assert(kOps <= 32, "one lane per TMA box");
@@ -181,6 +190,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
       store_row_fp16_swz<HD>(q_tile, Cfg::kQHalfBytes, r, x, lane, !live);
     }
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // (long since satisfied: the ring cannot fill before it)
   named_bar_sync(2, NW * 32);  // the whole Q tile is written before any warp reads its fragments
   const int g = lane >> 2, tq = lane & 3;
   uint32_t qa[HD / 16][4];
@@ -331,6 +341,7 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
   // a kernel queued behind this one with programmatic stream serialisation (the output projection's GEMV) may start
   // its weight prefetch now; it still waits for this grid to finish before it reads the attention output
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the decode grid in front has written the partials
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int ctx = min(a.ctx_lens[b], a.max_chunks * a.chunk_tokens);  // clamped (and reported) like the decode kernel
   const int n = (ctx + a.chunk_tokens - 1) / a.chunk_tokens;

@@ -40,7 +40,21 @@ struct PrefillTcArgs {
   // over NVLink, so the all-gather of head outputs rides along with the compute.
   void* bcast[7];
   int32_t n_bcast;
+  // 1: the raw query rows of the CTA are fetched by ONE tiled TMA load into the (still idle) K/V ring and the prologue
+  // reads them from shared memory; needs contiguous, 16-byte aligned head rows (set by the launcher with the map).
+  int32_t q_stage;
 };
+
+// 3-D tiled load global -> this CTA's shared memory (no multicast), completion counted on `bar`.
+// c0 = innermost (element) coordinate: must be a multiple of 16 bytes (0 here).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint64_t* bar, int32_t c0, int32_t c1,
+                                            int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -211,6 +225,33 @@ __device__ __forceinline__ void load_vec(const View& v, int64_t t, int64_t h, in
   }
 }
 
+// VEC consecutive dims of a raw row staged in shared memory (float32 or fp16), as one vector load.
+template <int VEC>
+__device__ __forceinline__ void load_vec_smem(uint32_t addr, bool f16, float* x) {
+  if (!f16) {
+    if constexpr (VEC == 4) {
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3]) : "r"(addr));
+    } else {
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(x[0]), "=f"(x[1]) : "r"(addr));
+    }
+  } else {
+    uint32_t lo, hi = 0;
+    if constexpr (VEC == 4) {
+      asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+    } else {
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(lo) : "r"(addr));
+    }
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    x[0] = a.x;
+    x[1] = a.y;
+    if constexpr (VEC == 4) {
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+      x[2] = b.x;
+      x[3] = b.y;
+    }
+  }
+}
+
 // 2^x for x <= 0 on the FMA / integer pipes (Cody-Waite split + degree-3 polynomial, relative error
 // below 8e-5, far under the fp16 rounding P gets next).  A quarter of the softmax exponentials go
 // through this instead of the special-function unit, which is the busiest unit of the kernel.
@@ -255,7 +296,12 @@ struct PrefillTcCfg {
   // stage, which the producer does not fill before the prologue has finished in that mode.
   static constexpr int kRowOff = kVOff + (kStagesV - 1) * kTileBytes;
   static constexpr int kBarOff = kVOff + kStagesV * kTileBytes;
-  static constexpr int kNumBars = 2 * kStagesK + 2 * kStagesV + 7;
+  // Raw query rows (256 rows of head_dim floats or halfs) staged by bulk copies: every ring stage except K stage 0,
+  // which takes the first K block meanwhile.  (fp32, head_dim 128: 128 KiB, exactly the four other stages.)
+  static constexpr int kQRawOff = kKOff + kTileBytes;
+  static constexpr int kQRawBytes = (kStagesK - 1 + kStagesV) * kTileBytes;
+  static_assert(kQRawBytes >= 256 * HD * 4, "the ring must hold 256 raw float32 query rows");
+  static constexpr int kNumBars = 2 * kStagesK + 2 * kStagesV + 8;
   static constexpr int kSmemBytes = 1024 + kBarOff + kNumBars * 8 + 32;  // + TMEM slot, abort flag, relay counters
   static constexpr int kThreads = 384;  // 12 warps: two softmax warpgroups + one warpgroup: TMA, MMA, two barrier scouts
   static constexpr int kTmemCols = 512;
@@ -295,11 +341,12 @@ __device__ __forceinline__ bool relay_wait(uint32_t* flag, uint32_t need, int32_
 template <int HD>
 __global__ void __launch_bounds__(384, 1)
     attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                           PrefillTcArgs ta) {
+                           const __grid_constant__ CUtensorMap q_map, PrefillTcArgs ta) {
   using Cfg = PrefillTcCfg<HD>;
   constexpr int SK = Cfg::kStagesK, SV = Cfg::kStagesV;
   const PrefillArgs& a = ta.p;
   const bool fast_prologue = a.q.ds == 1 && a.rope_dim == HD && ta.cs_table != nullptr;
+  const bool q_stage = fast_prologue && ta.q_stage != 0;
   // Heads vary fastest and query blocks run from the last (most keys) to the first, so the launch order is
   // longest-first over the WHOLE grid: the short blocks of every head fill the tail.  (With query blocks fastest the
   // last head's long blocks start last and run with most SMs idle: 0.71 ms instead of 0.51 ms at 8192 tokens.)
@@ -321,6 +368,7 @@ __global__ void __launch_bounds__(384, 1)
   uint64_t* p_full = bars + 2 * SK + 2 * SV + 2;  // [2]
   uint64_t* o_full = bars + 2 * SK + 2 * SV + 4;  // [2]
   uint64_t* q_ready = bars + 2 * SK + 2 * SV + 6;
+  uint64_t* q_raw = bars + 2 * SK + 2 * SV + 7;  // raw query rows have landed in the ring (staged prologue)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // Relay counters: what the scout warps have seen complete, as step counts: [0] K/V operands, [1] / [2] P of tile A / B.
@@ -354,6 +402,7 @@ __global__ void __launch_bounds__(384, 1)
       mbar_init(&o_full[t], 1);
     }
     mbar_init(q_ready, 256);
+    mbar_init(q_raw, 1);
     *abort_flag = (a.status != nullptr && *a.status != 0) ? 1 : 0;  // an earlier CTA already failed
     relay[0] = relay[1] = relay[2] = 0u;
     mbar_fence_init();
@@ -379,6 +428,15 @@ __global__ void __launch_bounds__(384, 1)
     if (lane == 0) {
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
+    }
+    if (q_stage && lane == 0) {
+      // The CTA's 256 raw query rows as ONE tiled load ({head_dim, 1 head, 256 tokens}; rows past the end of the
+      // prompt are zero-filled) into the ring stages that stay idle until the prologue is over; the softmax warps read
+      // them from shared memory.  (Through registers it took 32 loads per lane, ~4 us before the arithmetic could
+      // start; one bulk copy per row was slower still: the copy engine's rate is per request, not per byte.)
+      tma_prefetch_desc(&q_map);
+      mbar_arrive_expect_tx(q_raw, 256u * HD * (a.q.dtype == HL_DTYPE_F16 ? 2u : 4u));
+      tma_load_3d(base + Cfg::kQRawOff, &q_map, q_raw, 0, h, t0);
     }
     const int boxes_per_half = 128 / ta.box_rows;           // 8 or 1
     const int n_boxes = boxes_per_half * Cfg::kHalves;      // per K (or V) block: <= 16
@@ -409,8 +467,9 @@ __global__ void __launch_bounds__(384, 1)
         tma_load_2d(base + Cfg::kKOff + sk * Cfg::kTileBytes + dst_off, &k_map, &k_full[sk], hh * 64, row);
       // V block j
       if (j >= SV) tc_wait(&v_empty[sv], ((j / SV) - 1) & 1, a.status, 510 + sv, abort_flag);
-      // the general query prologue stages its rows in the last V stage: keep out until it is done
-      if (!fast_prologue && j == SV - 1) tc_wait(q_ready, 0, a.status, 515, abort_flag);
+      // the general query prologue stages its rows in the last V stage, the staged one in every stage but K stage 0:
+      // keep out until it is done
+      if ((!fast_prologue && j == SV - 1) || (q_stage && j == 0)) tc_wait(q_ready, 0, a.status, 515, abort_flag);
       if (lane == 0) mbar_arrive_expect_tx(&v_full[sv], Cfg::kTileBytes);
       __syncwarp();
       if (lane < n_boxes)
@@ -538,13 +597,15 @@ __global__ void __launch_bounds__(384, 1)
         const int tt0 = t0 + 128 * t + row0;
         const bool inter = a.rope_mode == HL_ROPE_INTERLEAVED;
         float x[32][VEC];
+        if (!q_stage) {
 #pragma unroll
-        for (int u = 0; u < 32; ++u) {
-          if (tt0 + u < a.n_tok) {
-            load_vec<VEC>(a.q, tt0 + u, h, d0, x[u]);
-          } else {
+          for (int u = 0; u < 32; ++u) {
+            if (tt0 + u < a.n_tok) {
+              load_vec<VEC>(a.q, tt0 + u, h, d0, x[u]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
+              for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
+            }
           }
         }
         int ai[NA];
@@ -563,6 +624,23 @@ __global__ void __launch_bounds__(384, 1)
         if (a.q_norm_w != nullptr) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) w[e] = a.q_norm_w[d0 + e];
+        }
+        if (q_stage) {
+          // staged rows: the cos / sin and weight loads above are already on their way; now the bulk copies must have
+          // landed.  A warp reads one row as 32 contiguous vectors (no bank conflicts).
+          tc_wait(q_raw, 0, a.status, 545, abort_flag);
+          const bool f16 = a.q.dtype == HL_DTYPE_F16;
+          const uint32_t row_bytes = HD * (f16 ? 2u : 4u);
+          const uint32_t src0 = base + Cfg::kQRawOff + (128 * t + row0) * row_bytes + d0 * (f16 ? 2u : 4u);
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            if (tt0 + u < a.n_tok) {
+              load_vec_smem<VEC>(src0 + u * row_bytes, f16, x[u]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
+            }
+          }
         }
         // Two warps share a scheduler here, so latency is hidden by independent instructions of ONE warp: the rows
         // are worked on eight at a time (while the later rows are still on their way from memory), and every step
@@ -921,9 +999,33 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
   if (rc != HL_OK) return rc;
   const bool wide = kv->block_tokens % 128 == 0;
   ta.box_rows = wide ? 128 : 16;
+  CUtensorMap q_map{};
+  {
+    // TMA staging of the raw query rows: contiguous head rows whose every start is 16-byte aligned, described by a
+    // 3-D map {head_dim, heads, tokens} over the caller's view (any token / head stride order)
+    const uint64_t el = a.q.dtype == HL_DTYPE_F16 ? 2 : 4;
+    static const bool no_stage = getenv("HL_B200_NO_QSTAGE") != nullptr;
+    ta.q_stage = !no_stage && a.q.ds == 1 && a.rope_dim == HD && reinterpret_cast<uintptr_t>(a.q.ptr) % 16 == 0 &&
+                 a.q.ts > 0 && a.q.hs > 0 && (a.q.ts * el) % 16 == 0 && (a.q.hs * el) % 16 == 0;
+    if (ta.q_stage) {
+      typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(a.n_head), static_cast<cuuint64_t>(a.n_tok)};
+      cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.q.hs) * el, static_cast<cuuint64_t>(a.q.ts) * el};
+      cuuint32_t box[3] = {static_cast<cuuint32_t>(HD), 1, 256};
+      cuuint32_t estr[3] = {1, 1, 1};
+      const CUresult r = reinterpret_cast<EncodeFn>(ctx->encode_tiled)(
+          &q_map, a.q.dtype == HL_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+          const_cast<void*>(a.q.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) ta.q_stage = 0;  // a view the copy engine cannot describe: the register prologue takes it
+    }
+    if (!ta.q_stage) q_map = wide ? kv->k_map128[layer] : kv->k_map[layer];  // a valid map; never used by the kernel then
+  }
   dim3 grid(a.n_head, (a.n_tok + 255) / 256);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(wide ? kv->k_map128[layer] : kv->k_map[layer],
-                                                              wide ? kv->v_map128[layer] : kv->v_map[layer], ta);
+                                                              wide ? kv->v_map128[layer] : kv->v_map[layer], q_map, ta);
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;

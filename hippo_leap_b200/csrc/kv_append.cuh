@@ -26,6 +26,11 @@ struct AppendArgs {
 template <int HD>
 __global__ void __launch_bounds__(128) kv_append_kernel(AppendArgs a) {
   __shared__ float rows[4][HD];
+  // With programmatic stream serialisation this grid first waits for the kernel in front, which produced the K / V rows
+  // it reads -- and the query rows the attention kernel behind it reads in ITS prologue, so only now may that kernel
+  // start (its set-up and query prologue then overlap this append; it waits for this grid before it touches the cache).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (row >= static_cast<int64_t>(a.n_tok) * a.n_head_kv) return;
