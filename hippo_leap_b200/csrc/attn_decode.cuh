@@ -347,13 +347,37 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
   const int n = (ctx + a.chunk_tokens - 1) / a.chunk_tokens;
   if (n <= 1) return;  // the decode kernel already wrote the final row (or zeroed it: empty context)
   const int64_t p0 = (static_cast<int64_t>(b) * a.n_head + h) * a.max_chunks;
-  float M = -INFINITY;
-  for (int ci = 0; ci < n; ++ci) M = fmaxf(M, a.part_ml[(p0 + ci) * 2]);
-  float L = 0.f, acc = 0.f;
-  for (int ci = 0; ci < n; ++ci) {
-    const float f = exp2f(a.part_ml[(p0 + ci) * 2] - M);
-    L += a.part_ml[(p0 + ci) * 2 + 1] * f;
-    acc += a.part_o[(p0 + ci) * HD + d] * f;
+  // Eight partials per trip: their (max, sum) pairs and this thread's output element are all requested before any is
+  // used, so a trip costs one L2 round trip.  (One partial per trip, each load waited for before the next was issued,
+  // made this pass a chain of n round trips: longer than the decode kernel itself for a single 2k-token sequence.)
+  float M = -INFINITY, L = 0.f, acc = 0.f;
+  for (int base = 0; base < n; base += 8) {
+    float m8[8], l8[8], o8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool ok = base + i < n;
+      const int64_t pi = p0 + (ok ? base + i : 0);
+      const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + pi * 2);
+      const float o = a.part_o[pi * HD + d];
+      m8[i] = ok ? ml.x : -INFINITY;   // a missing partial weighs exp2(-inf) = 0
+      l8[i] = ok ? ml.y : 0.f;
+      o8[i] = ok ? o : 0.f;
+    }
+    float Mt = M;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) Mt = fmaxf(Mt, m8[i]);
+    if (base > 0) {  // bring what was summed so far to the new maximum
+      const float f = exp2f(M - Mt);
+      L *= f;
+      acc *= f;
+    }
+    M = Mt;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = exp2f(m8[i] - M);
+      L += l8[i] * f;
+      acc += o8[i] * f;
+    }
   }
   decode_store(a, b, h, d, apply_gate(a.gate, b, h, d, acc / L));
 }

@@ -95,20 +95,56 @@ __global__ void gather_qkv_kernel(const float* __restrict__ eq, const float* __r
 // x = sum over layers of the last token's attention output (layer order, float32 adds);
 // logits[v] = sum_d x[d] * wout[d][v], d ascending, separate multiply and add (no FMA contraction),
 // i.e. the k-innermost float32 accumulation of the reference's CPU matmul (tensor.nim:77-80).
-__global__ void logits_kernel(const float* __restrict__ outs, int n_layer, int64_t layer_stride, int q_dim,
-                              const float* __restrict__ wout, int n_vocab, float* __restrict__ logits) {
-  extern __shared__ float x[];
+//
+// One thread owns one logit and adds its q_dim products strictly in order (that order is the result), so a block
+// cannot split the sum; what it can do is feed it: a block of 256 threads serves 32 logits, all 256 fetch the next
+// [64 d][32 v] tile of wout (coalesced 128-byte rows, eight loads in flight per thread) while the 32 owning threads
+// run down the current tile in shared memory.  (With one logit per thread and nothing else -- two blocks for a
+// 512-word vocabulary -- each warp had four loads in flight and the projection took longer than all sixteen attention
+// layers of a decode step together.)
+constexpr int kLogitsV = 32, kLogitsD = 64;
+__global__ void __launch_bounds__(256) logits_kernel(const float* __restrict__ outs, int n_layer, int64_t layer_stride,
+                                                     int q_dim, const float* __restrict__ wout, int n_vocab,
+                                                     float* __restrict__ logits) {
+  extern __shared__ float x[];                       // [q_dim] summed layer outputs
+  __shared__ float tile[2][kLogitsD][kLogitsV];      // two tiles of wout, 8 KiB each
   for (int d = threadIdx.x; d < q_dim; d += blockDim.x) {
     float acc = outs[d];
     for (int l = 1; l < n_layer; ++l) acc = __fadd_rn(acc, outs[l * layer_stride + d]);
     x[d] = acc;
   }
-  __syncthreads();
-  const int v = blockIdx.x * blockDim.x + threadIdx.x;
-  if (v >= n_vocab) return;
+  const int v0 = blockIdx.x * kLogitsV;
+  const int c = threadIdx.x % kLogitsV, r0 = threadIdx.x / kLogitsV;  // this thread loads column c of rows r0, r0 + 8, ...
+  const bool col_ok = v0 + c < n_vocab;
+  float reg[kLogitsD / 8];
+  auto fetch = [&](int d0) {
+#pragma unroll
+    for (int i = 0; i < kLogitsD / 8; ++i) {
+      const int d = d0 + r0 + 8 * i;
+      reg[i] = (col_ok && d < q_dim) ? wout[static_cast<int64_t>(d) * n_vocab + v0 + c] : 0.f;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < kLogitsD / 8; ++i) tile[buf][r0 + 8 * i][c] = reg[i];
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();  // x and the first tile are in place
   float acc = 0.f;
-  for (int d = 0; d < q_dim; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d], wout[static_cast<int64_t>(d) * n_vocab + v]));
-  logits[v] = acc;
+  int buf = 0;
+  for (int d0 = 0; d0 < q_dim; d0 += kLogitsD) {
+    const bool more = d0 + kLogitsD < q_dim;
+    if (more) fetch(d0 + kLogitsD);                  // in flight while the owners add
+    if (threadIdx.x < kLogitsV) {
+      const int n = min(kLogitsD, q_dim - d0);
+      for (int d = 0; d < n; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d0 + d], tile[buf][d][threadIdx.x]));
+    }
+    if (more) stash(buf ^ 1);
+    __syncthreads();
+    buf ^= 1;
+  }
+  if (threadIdx.x < kLogitsV && v0 + threadIdx.x < n_vocab) logits[v0 + threadIdx.x] = acc;
 }
 
 // first maximal index wins, as argmaxLast (src/hippo_leap/sampling.nim:13-19)
@@ -231,8 +267,7 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, hl_kv_cache* cache, bo
       B_TRY(hl_b200_attn_prefill(g.ctx, kv, l, &s, &qv, n, pos0, g.table_d, kv->num_blocks, &ov, nullptr));
     }
   }
-  const int threads = 256;
-  logits_kernel<<<(g.hp.n_vocab + threads - 1) / threads, threads, qd * sizeof(float), st>>>(
+  logits_kernel<<<(g.hp.n_vocab + kLogitsV - 1) / kLogitsV, 256, qd * sizeof(float), st>>>(
       g.out + static_cast<int64_t>(n - 1) * qd, g.hp.n_layer, layer_stride, qd, g.wout, g.hp.n_vocab, g.logits_d);
   g.ctx->launches += 1;
   B_CUDA(cudaGetLastError());
