@@ -31,7 +31,7 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
-NCU_DECODE_TRAFFIC_RATIO = 1006.9 / 997.376  # ncu DRAM traffic / algorithmic bytes of the decode + combine launch
+NCU_DECODE_TRAFFIC_RATIO = 1005.96 / 997.376  # ncu DRAM traffic / algorithmic bytes of the decode + combine launch
 METRIC = "decode_attn_tok_per_s"
 UNIT = "tok/s"
 
@@ -217,7 +217,7 @@ def timed_loop(torch, fn, steps):
 
 # DRAM bytes per launch of the prefill kernels from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum; the
 # summaries under profiles/ give the commands).  None: not captured for that configuration.
-PREFILL_NCU_TRAFFIC = {3: 170.1e6 + 43.7e6}
+PREFILL_NCU_TRAFFIC = {3: 170.6e6 + 42.7e6, 5: 3770.3e6 + 514.8e6}
 
 
 def median_ms(torch, fn, n, min_sample_ms=2.0):
@@ -300,7 +300,7 @@ def extras_single_gpu(ctx, torch, device, peaks, quick, configs=(2, 3, 5), cpu=T
         ms = median_ms(torch, run, 3)
         sampler = ClockSampler(device.index or 0)
         sampler.start()
-        k_sus = max(8, int(500.0 / ms))
+        k_sus = 8 if quick else max(8, int(500.0 / ms))  # (the quick form is the small profiling target: few launches)
         timed_loop(torch, run, k_sus // 2)                      # bring the power governor to its steady state
         ms_sus = timed_loop(torch, run, k_sus // 2) / (k_sus // 2)
         clocks = sampler.stop()
@@ -874,8 +874,8 @@ def main():
                 for r, x in enumerate(per)]
     slow = max(per_rank, key=lambda e: e["ms_per_launch"])
     achieved = slow["gbs"]
-    # ncu (profiles/attn_decode_config4.md): 1006.9 MB of DRAM traffic per launch for the 997.4 MB one-GPU workload,
-    # i.e. 1.0096 x the algorithmic bytes; a rank's share of a larger set scales with its algorithmic bytes
+    # ncu (the decode summary under profiles/): 1006.0 MB of DRAM traffic per launch for the 997.4 MB one-GPU workload,
+    # i.e. 1.0086 x the algorithmic bytes; a rank's share of a larger set scales with its algorithmic bytes
     roofline = {"bound": "hbm", "kernel": "attn_decode_kernel<128,4,3> + attn_combine_kernel<128>",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_src": peaks["src"], "traffic": NCU_DECODE_TRAFFIC_RATIO * slow["algorithmic_bytes_per_launch"],
@@ -936,7 +936,11 @@ def main():
             "ms_per_step_each_repeat": [m / args.steps for m in region_ms], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV, f32 accumulate", "data": "synthetic",
             "config": workload_config(cfg, world),
-            "hbm_gbs": achieved, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "hbm_gbs": achieved,
+            # tok/s counts sequences, the work is KV bytes: the whole job's algorithmic bytes per second say how the
+            # ranks' shares compare (a 64-sequence draw of ctx ~ U[512, 8192] varies by +-6 % in bytes)
+            "kv_gbs_aggregate": sum(e["algorithmic_bytes_per_launch"] for e in per_rank) / (ms_total / args.steps * 1e-3) / 1e9,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps, "ms_per_step_each_repeat": [m / args.steps for m in e2e_ms],
                     "call": "hl_b200_decode_step_host (pinned float32 host q / k / v in, host out, every step)"},

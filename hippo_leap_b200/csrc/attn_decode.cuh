@@ -356,12 +356,15 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(DecodeArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const bool ok = base + i < n;
-      const int64_t pi = p0 + (ok ? base + i : 0);
-      const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + pi * 2);
-      const float o = a.part_o[pi * HD + d];
-      m8[i] = ok ? ml.x : -INFINITY;   // a missing partial weighs exp2(-inf) = 0
-      l8[i] = ok ? ml.y : 0.f;
-      o8[i] = ok ? o : 0.f;
+      const int64_t pi = p0 + base + i;
+      m8[i] = -INFINITY;  // a missing partial weighs exp2(-inf) = 0
+      l8[i] = o8[i] = 0.f;
+      if (ok) {           // (predicated loads: nothing is fetched for a missing partial)
+        const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + pi * 2);
+        m8[i] = ml.x;
+        l8[i] = ml.y;
+        o8[i] = a.part_o[pi * HD + d];
+      }
     }
     float Mt = M;
 #pragma unroll
