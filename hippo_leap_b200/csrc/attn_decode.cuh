@@ -40,6 +40,7 @@ struct DecodeArgs {
   // with plain stores over NVLink, so the all-gather of head outputs needs no collective kernel.
   void* bcast[7];
   int32_t n_bcast;
+  int32_t early_q;  // 1: the query rows are known to be complete before this grid can start (read before the wait)
 };
 
 // One output element to the local destination and to every broadcast destination.
@@ -83,7 +84,8 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   // (decode always attends at least the new token's own key) is reported and the output row is zeroed.
   // Launched with programmatic stream serialisation this grid starts while the kernel in front (the KV append of the
   // same step) is still running.  What that kernel writes -- the cache -- is only touched after griddepcontrol.wait;
-  // the barrier set-up and the query prologue run before it.  Every thread passes a wait before it exits, so that a
+  // the barrier set-up runs before it, and so does the query prologue when the caller vouches for the query rows
+  // (early_q: the library's own backends, where the append always sits between the projection and this kernel).  Every thread passes a wait before it exits, so that a
   // grid queued behind this one can rely on everything in front of this one having completed too.
   int ctx = a.ctx_lens[b];
   if (ctx > a.max_chunks * a.chunk_tokens) {
@@ -175,6 +177,7 @@ __global__ void __launch_bounds__((NW + 1) * 32)
   // ================= consumer warps =================
   // ---- Q prologue (while the first K/V stages are in flight): G rows -> norm -> RoPE at pos = ctx-1
   //      -> fp16 swizzled tile (rows >= G zero)
+  if (!a.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");  // the query rows may come from the grid in front
   {
     const int pos = ctx - 1;
     for (int r = warp; r < 16; r += NW) {

@@ -43,6 +43,7 @@ struct PrefillTcArgs {
   // 1: the raw query rows of the CTA are fetched by ONE tiled TMA load into the (still idle) K/V ring and the prologue
   // reads them from shared memory; needs contiguous, 16-byte aligned head rows (set by the launcher with the map).
   int32_t q_stage;
+  int32_t early_q;  // 1: the query rows are known to be complete before this grid can start (read before the wait)
 };
 
 // 3-D tiled load global -> this CTA's shared memory (no multicast), completion counted on `bar`.
@@ -351,6 +352,7 @@ __global__ void __launch_bounds__(384, 1)
   // longest-first over the WHOLE grid: the short blocks of every head fill the tail.  (With query blocks fastest the
   // last head's long blocks start last and run with most SMs idle: 0.71 ms instead of 0.51 ms at 8192 tokens.)
   // Neighbouring CTAs are the query heads of one KV head, so they share K/V tiles in L2.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a kernel queued behind may begin its own set-up
   const int q_blk = gridDim.y - 1 - blockIdx.y;
   const int h = blockIdx.x;
   const int kvh = h / a.group;
@@ -429,6 +431,7 @@ __global__ void __launch_bounds__(384, 1)
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
     }
+    if (!ta.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");  // the query rows may come from the grid in front
     if (q_stage && lane == 0) {
       // The CTA's 256 raw query rows as ONE tiled load ({head_dim, 1 head, 256 tokens}; rows past the end of the
       // prompt are zero-filled) into the ring stages that stay idle until the prologue is over; the softmax warps read
@@ -438,6 +441,9 @@ __global__ void __launch_bounds__(384, 1)
       mbar_arrive_expect_tx(q_raw, 256u * HD * (a.q.dtype == HL_DTYPE_F16 ? 2u : 4u));
       tma_load_3d(base + Cfg::kQRawOff, &q_map, q_raw, 0, h, t0);
     }
+    // Launched with programmatic stream serialisation this grid may start while the kernel in front -- the KV append of
+    // the same prompt -- is still running: set-up and the query prologue do not depend on it, the cache does.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int boxes_per_half = 128 / ta.box_rows;           // 8 or 1
     const int n_boxes = boxes_per_half * Cfg::kHalves;      // per K (or V) block: <= 16
     const int box_bytes = ta.box_rows * 128;
@@ -580,6 +586,7 @@ __global__ void __launch_bounds__(384, 1)
     const uint32_t tO = tmem + lane_sel + Cfg::kColO + t * HD;
 
     // ---- Q prologue: this warp prepares rows [32*(warp&3), +32) of tile t ----
+    if (!ta.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");  // query rows, cos / sin table, norm weights
     {
       const uint32_t q_tile = base + Cfg::kQOff + t * Cfg::kTileBytes;
       constexpr int VEC = HD / 32;
@@ -842,6 +849,7 @@ __global__ void __launch_bounds__(384, 1)
     if (n_blk[t] > 0) softmax_block(std::true_type{}, 0);
     for (int j = 1; j < n_blk[t]; ++j) softmax_block(std::false_type{}, j);
     // ---- epilogue: O / l -> out ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (satisfied long ago; orders the output stores behind the grid in front)
     if (n_blk[t] > 0) {
       tc_wait(&o_full[t], 0, a.status, 550 + t, abort_flag);
       tc_fence_after();
@@ -958,6 +966,7 @@ static int32_t hl_prefill_tc_fill_args(hl_ctx* ctx, hl_kv* kv, const hl::Prefill
   ta.p = a;
   ta.cs_table = nullptr;
   ta.n_bcast = n_bcast;
+  ta.early_q = ctx->chain_pdl ? 1 : 0;
   for (int i = 0; i < n_bcast; ++i) ta.bcast[i] = bcast[i];
   if (a.rope_dim == head_dim) {
     if (ctx->cs_len < n_pos || ctx->cs_half != half) {
@@ -1024,8 +1033,9 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
     if (!ta.q_stage) q_map = wide ? kv->k_map128[layer] : kv->k_map[layer];  // a valid map; never used by the kernel then
   }
   dim3 grid(a.n_head, (a.n_tok + 255) / 256);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, ctx->stream>>>(wide ? kv->k_map128[layer] : kv->k_map[layer],
-                                                              wide ? kv->v_map128[layer] : kv->v_map[layer], q_map, ta);
+  HL_CUDA(ctx, launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, ctx->stream,
+                          wide ? kv->k_map128[layer] : kv->k_map[layer], wide ? kv->v_map128[layer] : kv->v_map[layer],
+                          q_map, ta));
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;

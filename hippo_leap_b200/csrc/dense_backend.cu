@@ -76,6 +76,9 @@ int32_t ensure_ctx(int device) {
   int32_t rc = hl_b200_create(device, nullptr, &d.ctx);
   if (rc != HL_OK) return dfail(rc, "hl_b200_create failed: no usable sm_100 device (no CPU fallback exists)");
   d.device = device;
+  // this backend always queues the KV append between the kernel that produces the query rows and the attention kernel:
+  // the attention kernels may start their query prologue while the append runs
+  d.ctx->chain_pdl = true;
   return HL_OK;
 }
 

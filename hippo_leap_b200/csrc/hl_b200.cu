@@ -82,24 +82,6 @@ int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int
   return HL_OK;
 }
 
-// Launch with programmatic stream serialisation: the grid may start while its predecessor in the stream drains; the
-// kernels order themselves with griddepcontrol.wait.  HL_B200_NO_PDL in the environment restores plain launches.
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
-  static const bool no_pdl = getenv("HL_B200_NO_PDL") != nullptr;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = no_pdl ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-}
-
 namespace {
 View to_view(const hl_view* v) { return View{v->ptr, v->dtype, v->tok_stride, v->head_stride, v->dim_stride}; }
 inline int32_t check_view(hl_ctx* ctx, const hl_view* v, const char* name) { return hl_check_view(ctx, v, name); }
@@ -436,16 +418,10 @@ static int32_t launch_append(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_att
   const int64_t rows = static_cast<int64_t>(n_tok) * s->n_head_kv;
   const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
-  // one-token steps are launch-latency-bound: let the append overlap the tail of the kernel in front and the decode
-  // kernel behind overlap the append (whole-prompt appends gain nothing and keep the plain launch)
-  if (batch_mode) {
-    HL_CUDA(ctx, s->head_dim == 64 ? launch_pdl(kv_append_kernel<64>, dim3(grid), dim3(128), 0, ctx->stream, a)
-                                   : launch_pdl(kv_append_kernel<128>, dim3(grid), dim3(128), 0, ctx->stream, a));
-  } else if (s->head_dim == 64) {
-    kv_append_kernel<64><<<grid, 128, 0, ctx->stream>>>(a);
-  } else {
-    kv_append_kernel<128><<<grid, 128, 0, ctx->stream>>>(a);
-  }
+  // the append may overlap the tail of the kernel in front, and the attention kernel behind (decode or prefill) starts
+  // its set-up and query prologue during the append
+  HL_CUDA(ctx, s->head_dim == 64 ? launch_pdl(kv_append_kernel<64>, dim3(grid), dim3(128), 0, ctx->stream, a)
+                                 : launch_pdl(kv_append_kernel<128>, dim3(grid), dim3(128), 0, ctx->stream, a));
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;
@@ -559,6 +535,7 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
   a.max_blocks = max_blocks_per_seq;
   a.n_bcast = n_bcast;
   for (int i = 0; i < n_bcast; ++i) a.bcast[i] = bcast[i];
+  a.early_q = ctx->chain_pdl ? 1 : 0;
 
   rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <string>
 #include <vector>
@@ -32,6 +33,12 @@ struct hl_ctx {
   void* cs_table = nullptr;  // float2 [cs_len][cs_half]: (cos, sin) of float(pos) * theta_i
   int cs_len = 0, cs_half = 0;
   void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved through the runtime
+  // Set by the backends inside this library (hl_backend_*, hl_dense_*), whose call order guarantees that the KV append
+  // sits between the kernel that produced the query rows and the attention kernel: the attention kernels may then read
+  // the query rows BEFORE griddepcontrol.wait (their prologue overlaps the append).  Through the public operators the
+  // caller's kernel order is unknown -- the query rows may come from the kernel directly in front, and that kernel may
+  // let its dependents start early -- so there every input is read after the wait.
+  bool chain_pdl = false;
   int32_t decode_chunk = 0;
   int32_t prefill_kernel = 0;
   int64_t launches = 0;
@@ -60,6 +67,25 @@ int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_
 int32_t hl_linear_decode_fused(hl_ctx* ctx, int32_t mode, int32_t swiglu, const void* a, int64_t lda, const float* norm_w,
                                float eps, const void* w, int64_t ldw, void* out, int32_t out_dtype, int64_t ldo,
                                const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K);
+
+// Launch with programmatic stream serialisation: the grid may start while its predecessor in the stream drains; the
+// kernels order themselves with griddepcontrol.wait.  HL_B200_NO_PDL in the environment restores plain launches.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+  static const bool no_pdl = getenv("HL_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 #define HL_CUDA(ctx, expr)                                                                   \
   do {                                                                                       \

@@ -74,6 +74,9 @@ int32_t ensure_ctx(int device) {
   int32_t rc = hl_b200_create(device, nullptr, &g.ctx);
   if (rc != HL_OK) return bfail(rc, "hl_b200_create failed: no usable sm_100 device (no CPU fallback exists)");
   g.device = device;
+  // this backend always queues the KV append between the kernel that produces the query rows and the attention kernel:
+  // the attention kernels may start their query prologue while the append runs
+  g.ctx->chain_pdl = true;
   return HL_OK;
 }
 
