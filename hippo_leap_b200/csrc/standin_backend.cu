@@ -141,7 +141,12 @@ __global__ void __launch_bounds__(256) logits_kernel(const float* __restrict__ o
     if (more) fetch(d0 + kLogitsD);                  // in flight while the owners add
     if (threadIdx.x < kLogitsV) {
       const int n = min(kLogitsD, q_dim - d0);
-      for (int d = 0; d < n; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d0 + d], tile[buf][d][threadIdx.x]));
+      if (n == kLogitsD) {  // whole tile: unrolled, so the shared-memory loads run ahead of the chain of additions
+#pragma unroll
+        for (int d = 0; d < kLogitsD; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d0 + d], tile[buf][d][threadIdx.x]));
+      } else {
+        for (int d = 0; d < n; ++d) acc = __fadd_rn(acc, __fmul_rn(x[d0 + d], tile[buf][d][threadIdx.x]));
+      }
     }
     if (more) stash(buf ^ 1);
     __syncthreads();
