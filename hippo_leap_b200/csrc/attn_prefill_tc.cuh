@@ -7,14 +7,21 @@
 // core: while the softmax warps of one tile work on S = Q K^T, the MMA warp runs the other tile.
 //   warps 0-3  softmax of tile A  (thread r owns row r: TMEM lane r, no shuffles in the softmax)
 //   warps 4-7  softmax of tile B
-//   warp  8    TMA producer: K and V blocks of 128 keys from the paged cache, 128-byte swizzle
-//   warp  9    MMA issuer (one elected lane) and TMEM owner
+//   warp  8    TMA producer: K and V blocks of 128 keys from the paged cache, 128-byte swizzle; and, for
+//              contiguous aligned query rows, ONE tiled load of the CTA's 256 raw rows into the idle K/V ring
+//   warp  9    MMA issuer (one elected lane) and TMEM owner.  Inside the key loop it waits on no barrier (a
+//              barrier wait costs this thread ~250 cycles while its MMAs are queued) and steps its descriptors with
+//              one add per MMA (rebuilding them made the thread, not the tensor pipe, the bound)
+//   warps 10-11  barrier scouts: wait on the K/V and P barriers in the issuer's order and publish step counters in
+//              shared memory, which the issuer polls with acquire loads
 // TMEM (512 columns): S_A, S_B (128 fp32 columns each; P, as fp16 pairs, overwrites the first 64
 // columns of its S once the row has been read), O_A, O_B (head_dim columns each).
 //   S_t  = Q_t K_j^T    tcgen05.mma kind::f16, A and B from shared memory (K-major, SW128)
 //   O_t += P_t V_j      A from TMEM, B = V from shared memory as an MN-major SW128 operand
 // The running maximum is only raised when it grows by more than 2^8 (the O rescale in TMEM then
-// happens rarely); the final division by the row sum restores exactness.
+// happens rarely); the final division by the row sum restores exactness.  After a tile's first block the
+// exponentials therefore start at once against the running maximum, with the block's row maximum computed
+// beside them; a row that does need a higher maximum has its first half done again.
 // The query prologue (RMSNorm, RoPE from a cos/sin table built with full-precision sincosf, fp16)
 // is done by the softmax warps while the first K/V blocks are in flight.
 // Every wait is bounded; a timeout raises the status word, makes all later waits of the CTA fall
