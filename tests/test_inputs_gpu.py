@@ -181,3 +181,42 @@ def test_partial_rotary(hl_ctx, hd, rope_dim, rope_mode, kernel):
     assert np.abs(row[rope_dim:] - normed[rope_dim:].astype(np.float16).astype(np.float32)).max() <= 1e-3
     assert np.abs(row[:rope_dim] - normed[:rope_dim]).max() > 1e-2     # and the head of the row did rotate
     kv.destroy()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("kernel", [pytest.param(1, id="mma"), pytest.param(2, id="tcgen05")])
+def test_head_major_query_and_output_views(hl_ctx, dtype, kernel):
+    """Q, K, V and the output held head-major ([heads][tokens][head_dim]: the token stride is SMALLER than the head
+    stride) and passed as [tokens][heads][head_dim] views -- the layout the head-sharded runners write -- through append,
+    prefill (whichever query prologue the view gets: staged by TMA when the copy engine can describe it, registers
+    otherwise) and decode, against the oracle."""
+    hd, n_head, n_head_kv, S, bt = 128, 8, 2, 700, 16
+    g = np.random.Generator(np.random.PCG64([S, 17]))
+    theta = hl.theta_table(hd, 5e5)
+    hl_ctx.set_rope(theta)
+    shape = hl.AttnShape(n_head, n_head_kv, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+    q, k, v = (g.standard_normal((S + 1, h_, hd), dtype=np.float32) for h_ in (n_head, n_head_kv, n_head_kv))
+    if dtype == torch.float16:
+        q, k, v = _half_round(q, k, v)
+    nb = (S + 1 + bt - 1) // bt
+    table = torch.from_numpy(g.permutation(nb).astype(np.int32)).cuda()
+    kv = hl_ctx.kv_create(1, n_head_kv, hd, bt, nb)
+    # head-major storage, token-major views
+    hq, hk, hv = (torch.from_numpy(x).cuda().to(dtype).permute(1, 0, 2).contiguous() for x in (q, k, v))
+    tq, tk, tv = (x.permute(1, 0, 2) for x in (hq, hk, hv))
+    assert tq.stride(0) < tq.stride(1)
+    out_hm = torch.full((n_head, S, hd), float("nan"), dtype=torch.float32, device="cuda")
+    hl_ctx.set_tuning(0, kernel)
+    try:
+        hl_ctx.kv_append_seq(kv, 0, shape, tk[:S], tv[:S], 0, table)
+        hl_ctx.attn_prefill(kv, 0, shape, tq[:S], 0, table, out_hm.permute(1, 0, 2))
+    finally:
+        hl_ctx.set_tuning(0, 0)
+    want = oracle_seq(q[:S], k[:S], v[:S], theta=theta, rope_mode=1)
+    assert_parity(out_hm.permute(1, 0, 2).cpu().numpy(), want, "head-major views, prefill")
+    ctx_lens = torch.tensor([S + 1], dtype=torch.int32, device="cuda")
+    hl_ctx.kv_append_batch(kv, 0, shape, tk[S:], tv[S:], ctx_lens, table.view(1, -1))
+    dec = hl_ctx.attn_decode(kv, 0, shape, tq[S:], ctx_lens, S + 1, table.view(1, -1))
+    want_d = oracle_seq(q[S:], k[S:], v[S:], theta=theta, rope_mode=1, prefix=(k[:S], v[:S]))
+    assert_parity(dec.cpu().numpy(), want_d, "head-major views, decode")
+    kv.destroy()
