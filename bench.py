@@ -10,8 +10,8 @@ sequence: KV append + split-KV attention + combine, for one attention layer.  Th
   python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
   python bench.py --impl reference ...                     (CPU oracle on the host cores)
 
-With N > 1 ONE seeded set of 64 * N sequences is dealt to the ranks greedy longest-first, so every rank streams
-about the same number of KV bytes (weak scaling, no collective on the data path); every timed region is bracketed
+With N > 1 the workload is N instances of the 64-sequence set, dealt to the ranks greedy longest-first as one set of
+64 * N sequences: every rank streams the KV bytes of the one-GPU workload (weak scaling, no collective on the data path); every timed region is bracketed
 by a barrier + synchronize, the maximum over ranks is taken, and the median of several such regions is reported.
 One JSON line is printed by rank 0.
 """
@@ -95,9 +95,10 @@ class ClockSampler:
 # workloads
 # ------------------------------------------------------------------------------------------------
 def setup_decode(ctx, cfg, rank, world, device):
-    """This rank's share of the ONE seeded set of `cfg.batch * world` sequences (greedy longest-first on context
-    length: equal KV bytes per rank); paged pools filled (through the append kernel) with seeded N(0,1) K/V;
-    returns everything a decode step needs.  At world 1 the share is the whole 64-sequence set."""
+    """This rank's share of the set of `cfg.batch * world` sequences -- `world` instances of the seeded 64-sequence
+    workload dealt greedy longest-first on context length: every rank gets one sequence of each length, i.e. the KV
+    bytes of the one-GPU workload; paged pools filled (through the append kernel) with this rank's own seeded N(0,1)
+    K/V in its own page order; returns everything a decode step needs."""
     import torch
 
     import hippo_leap_b200 as hl
@@ -200,8 +201,8 @@ def workload_config(cfg, n_gpus):
             "n_head": cfg.n_head, "n_head_kv": cfg.n_head_kv, "head_dim": cfg.head_dim,
             "sequences_per_gpu": cfg.batch, "ctx_range": list(cfg.ctx_range), "kv": "paged fp16",
             "block_tokens": cfg.block_tokens,
-            "sharding": f"one seeded set of {cfg.batch * n_gpus} sequences dealt to {n_gpus} GPU(s) greedy longest-first "
-                        "(equal KV bytes per GPU), no collective",
+            "sharding": f"{n_gpus} instance(s) of the seeded 64-sequence set = {cfg.batch * n_gpus} sequences, dealt to {n_gpus} "
+                        "GPU(s) greedy longest-first (every GPU carries the KV bytes of the one-GPU workload), no collective",
             "l2": "KV working set ~1.1 GB per GPU >> 126 MB L2 (no flush needed)"}
 
 
@@ -937,8 +938,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV, f32 accumulate", "data": "synthetic",
             "config": workload_config(cfg, world),
             "hbm_gbs": achieved,
-            # tok/s counts sequences, the work is KV bytes: the whole job's algorithmic bytes per second say how the
-            # ranks' shares compare (a 64-sequence draw of ctx ~ U[512, 8192] varies by +-6 % in bytes)
+            # tok/s counts sequences, the work is KV bytes: the whole job's algorithmic bytes per second
             "kv_gbs_aggregate": sum(e["algorithmic_bytes_per_launch"] for e in per_rank) / (ms_total / args.steps * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -121,10 +121,15 @@ def shard_longest_first(ctx_lens: np.ndarray, n_ranks: int):
 
 
 def gen_sharded_ctx_lens(cfg: AttnConfig, world: int):
-    """The batched-decode workload at ``world`` GPUs: ONE seeded set of ``cfg.batch * world`` sequences (its first
-    ``cfg.batch`` values are the one-GPU set), assigned to ranks greedy longest-first so that every rank streams
-    about the same number of KV bytes.  Returns (all context lengths, list of per-rank index lists)."""
-    all_ctx = gen_ctx_lens(cfg, batch=cfg.batch * world)
+    """The batched-decode workload at ``world`` GPUs under weak scaling: ``world`` instances of the seeded
+    ``cfg.batch``-sequence workload as ONE set of ``cfg.batch * world`` sequences, dealt to the ranks greedy longest-first.
+    Every instance has the same context lengths (each rank fills them with its own K/V data and page order), so the
+    deal gives every rank one sequence of each length: per-GPU work -- KV bytes, which is what a decode step costs, not
+    sequences -- is the same at every ``world``, which is what weak scaling means.  (Fresh draws per instance differ by
+    +-6 % in bytes from one 64-sequence draw to the next, and the one-GPU draw happens to be 13 % lighter than the mean:
+    tok/s per GPU would then fall with ``world`` for no reason but the draw.)
+    Returns (all context lengths, list of per-rank index lists)."""
+    all_ctx = np.tile(gen_ctx_lens(cfg), world)
     return all_ctx, shard_longest_first(all_ctx, world)
 
 
