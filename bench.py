@@ -916,9 +916,14 @@ def main():
             extra["linear_f16"] = extra_linear(ctx, torch, device, peaks)
             extra["dense_llama32_1b"] = extra_dense_model(torch, local_rank)
         if cfg.n_head_kv % world == 0:
-            extra["config5_head_sharded_prefill"] = extra_head_sharded_prefill(ctx, torch, dist, device, rank, world,
-                                                                               peaks)
-            extra["config4_head_sharded_decode"] = extra_head_sharded_decode(ctx, torch, dist, device, rank, world, peaks)
+            # side measurements after the headline: a failure here (it would be the same on every rank: a missing
+            # symmetric-memory feature, an allocation) is recorded and must not cost the line above
+            for name, fn in (("config5_head_sharded_prefill", extra_head_sharded_prefill),
+                             ("config4_head_sharded_decode", extra_head_sharded_decode)):
+                try:
+                    extra[name] = fn(ctx, torch, dist, device, rank, world, peaks)
+                except Exception as e:  # noqa: BLE001
+                    extra[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
