@@ -60,6 +60,7 @@ SYMBOLS = {
     "hl_b200_prefill_host": (_i32, [_vp, _vp, _i32, _shape_p, _f32p, _f32p, _f32p, _i32, _i32, _vp, _i32, _f32p, _f32p]),
     "hl_b200_decode_step_host": (_i32, [_vp, _vp, _i32, _shape_p, _f32p, _f32p, _f32p, _i32, _vp, _i32, _vp, _i32, _f32p, _f32p]),
     "hl_b200_linear_f16": (_i32, [_vp, _vp, C.c_int64, _vp, C.c_int64, _vp, _i32, C.c_int64, _vp, C.c_int64, _i32, _i32, _i32, _f32p]),
+    "hl_b200_linear_f16_silu": (_i32, [_vp, _vp, C.c_int64, _vp, C.c_int64, _vp, C.c_int64, _i32, _i32, _i32, _f32p]),
     "hl_b200_selftest_wait_timeout": (_i32, [_vp, _i32]),
     "hl_b200_set_tuning": (_i32, [_vp, _i32, _i32]),
 }

@@ -277,10 +277,25 @@ int32_t forward(const int32_t* tokens_h, int n, int pos0, KvRef ref, bool decode
                                    HL_DTYPE_F32, E, d.x, E, n, E, F));
     } else {
       rmsnorm_rows_kernel<<<n, 256, 0, st>>>(d.x, d.ffn_norm + static_cast<size_t>(l) * E, E, hp.rms_eps, d.xn);
-      D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.gu, HL_DTYPE_F16, 2 * F,
-                               nullptr, 0, n, 2 * F, E, nullptr));
-      const int64_t total = static_cast<int64_t>(n) * F;
-      silu_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(d.gu, F, total, d.h);
+      static const bool no_fused_silu = getenv("HL_B200_NO_FUSED_SILU") != nullptr;  // for comparison runs
+      if (n > 128 && !no_fused_silu) {
+        // SiLU(gate) * up in the GEMM's epilogue: no fp16 [n, 2F] intermediate, no row kernel.  (Up to 128 rows the
+        // several-row projection kernel is the faster GEMM and keeps the two-step form.)
+        D_TRY(hl_b200_linear_f16_silu(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.h, F, n, 2 * F, E,
+                                      nullptr));
+        d.ctx->launches -= 1;
+      } else {
+        D_TRY(hl_b200_linear_f16(d.ctx, d.xn, E, d.wgu + static_cast<size_t>(l) * 2 * F * E, E, d.gu, HL_DTYPE_F16, 2 * F,
+                                 nullptr, 0, n, 2 * F, E, nullptr));
+        const int64_t total = static_cast<int64_t>(n) * F;
+        if ((total & 7) == 0 && ((reinterpret_cast<uintptr_t>(d.gu) | reinterpret_cast<uintptr_t>(d.h)) & 15) == 0) {
+          const int64_t total8 = total >> 3;
+          const int64_t want = (total8 + 255) / 256, cap = static_cast<int64_t>(d.ctx->n_sm) * 16;
+          silu_mul_vec8_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(d.gu, total8, d.h);
+        } else {
+          silu_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(d.gu, F, total, d.h);
+        }
+      }
       d.ctx->launches += 2;
       // x += h . Wdown^T   (naive.nim:4085-4086)
       D_TRY(hl_b200_linear_f16(d.ctx, d.h, F, d.wdown + static_cast<size_t>(l) * E * F, F, d.x, HL_DTYPE_F32, E, d.x, E, n, E,

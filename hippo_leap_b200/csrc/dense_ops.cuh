@@ -42,4 +42,24 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gu, int n_ffn, int64_
   h[idx] = silu_mul_f16(__low2half(p), __high2half(p));
 }
 
+// The same, eight outputs per thread: two 16-byte loads of (gate, up) pairs, one 16-byte store.  (One output per thread
+// -- a 4-byte load and a 2-byte store each -- ran at a quarter of the memory rate: 70 us for the 100 MB of a
+// 2048 x 8192 activation.)  gu and h contiguous, 16-byte aligned, total a multiple of 8.
+__global__ void silu_mul_vec8_kernel(const __half* __restrict__ gu, int64_t total8, __half* __restrict__ h) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 a = reinterpret_cast<const uint4*>(gu)[2 * i], b = reinterpret_cast<const uint4*>(gu)[2 * i + 1];
+    const uint32_t in[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2 p0 = *reinterpret_cast<const __half2*>(&in[2 * k]), p1 = *reinterpret_cast<const __half2*>(&in[2 * k + 1]);
+      const __half2 r = __halves2half2(silu_mul_f16(__low2half(p0), __high2half(p0)), silu_mul_f16(__low2half(p1), __high2half(p1)));
+      o[k] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    reinterpret_cast<uint4*>(h)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace hl

@@ -867,7 +867,25 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
   if (!a || !w || !out) return hl_fail(ctx, HL_ERR_ARG, "linear: null pointer");
   if (M <= 0 || N <= 0 || K <= 0) return hl_fail(ctx, HL_ERR_ARG, "linear: non-positive size");
   if (out_dtype != HL_DTYPE_F32 && out_dtype != HL_DTYPE_F16) return hl_fail(ctx, HL_ERR_ARG, "linear: bad out dtype");
+  return hl_linear_f16_impl(ctx, a, lda, w, ldw, out, out_dtype, ldo, resid, ldr, M, N, K, gpu_ms);
+}
+
+extern "C" int32_t hl_b200_linear_f16_silu(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* h,
+                                           int64_t ldh, int32_t M, int32_t N, int32_t K, float* gpu_ms) {
+  if (!ctx) return HL_ERR_ARG;
+  if (!a || !w || !h) return hl_fail(ctx, HL_ERR_ARG, "linear: null pointer");
+  if (M < 16 || N <= 0 || (N & 1) || K <= 0 || ldh < N / 2)
+    return hl_fail(ctx, HL_ERR_ARG, "linear (silu): needs M >= 16, even N and ldh >= N / 2");
+  return hl_linear_f16_impl(ctx, a, lda, w, ldw, h, hl::kLinearOutSiluPairs, N, nullptr, 0, M, N, K, gpu_ms, ldh);
+}
+
+int32_t hl_linear_f16_impl(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int32_t out_dtype,
+                           int64_t ldo, const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K, float* gpu_ms,
+                           int64_t ld_store) {
+  if (out_dtype != HL_DTYPE_F32 && out_dtype != HL_DTYPE_F16 && out_dtype != hl::kLinearOutSiluPairs)
+    return hl_fail(ctx, HL_ERR_ARG, "linear: bad out dtype");
   if (lda < K || ldw < K || ldo < N || (resid && ldr < N)) return hl_fail(ctx, HL_ERR_ARG, "linear: leading dimension too small");
+  if (ld_store > 0) ldo = ld_store;  // the pair form stores N / 2 columns per row
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
   LinearArgs g{};
   g.a = static_cast<const __half*>(a);
@@ -886,7 +904,8 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
   int32_t rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
   static const bool no_wide = getenv("HL_B200_NO_WIDE") != nullptr;
-  if (M >= 2 && M <= 128 && !no_wide && !(lda & 7) && !(ldw & 7) && !(reinterpret_cast<uintptr_t>(a) & 15) &&
+  const bool silu = out_dtype == hl::kLinearOutSiluPairs;  // implemented by the two tcgen05 GEMMs only (M >= 16)
+  if (M >= 2 && M <= 128 && !no_wide && !silu && !(lda & 7) && !(ldw & 7) && !(reinterpret_cast<uintptr_t>(a) & 15) &&
       !(reinterpret_cast<uintptr_t>(w) & 15)) {
     rc = launch_wide(ctx, g);
     if (rc != HL_OK) return rc;
@@ -911,7 +930,7 @@ extern "C" int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, c
     if ((lda & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
       return hl_fail(ctx, HL_ERR_ALIGN, "linear: A and W need 16-byte aligned bases and row strides (multiples of 8 halfs)");
     static const bool no_pair = getenv("HL_B200_GEMM_NO_PAIR") != nullptr;
-    if (M >= 512 && !no_pair) {
+    if (M >= 512 && (!no_pair || out_dtype == hl::kLinearOutSiluPairs)) {
       // 256 x 256 tiles on SM pairs (linear_f16_pair.cuh)
       using Cfg = LinearPairCfg;
       static bool configured2[16] = {};

@@ -87,6 +87,11 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// The body of hl_b200_linear_f16 with the internal output forms; ld_store > 0 overrides the stored row stride.
+int32_t hl_linear_f16_impl(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int32_t out_dtype,
+                           int64_t ldo, const float* resid, int64_t ldr, int32_t M, int32_t N, int32_t K, float* gpu_ms,
+                           int64_t ld_store = 0);
+
 #define HL_CUDA(ctx, expr)                                                                   \
   do {                                                                                       \
     cudaError_t e_ = (expr);                                                                 \

@@ -30,6 +30,32 @@ struct LinearArgs {
   int32_t* status;
 };
 
+// Internal value of LinearArgs::out_dtype (not part of the C ABI): fp16 output of N / 2 columns,
+// out[m][c] = fp16(silu(fp16 acc[m][2c]) * fp16 acc[m][2c + 1]): W's rows interleave gate and up, so accumulator columns
+// 2c and 2c + 1 are the two factors of output column c -- the value the separate row kernel computes from the fp16 GEMM
+// output, written directly (half the bytes, one launch fewer).  Both tcgen05 GEMMs implement it.
+constexpr int32_t kLinearOutSiluPairs = 100;
+
+// Epilogue store of that form for 32 accumulator columns starting at even column n of row m.
+__device__ __forceinline__ void store_silu_pairs32(const LinearArgs& g, int m, int n, int nv, const float (&v)[32]) {
+  __half* op = static_cast<__half*>(g.out) + static_cast<int64_t>(m) * g.ldo + (n >> 1);
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const __half2 r = __halves2half2(silu_mul_f16(__float2half_rn(v[i]), __float2half_rn(v[i + 1])),
+                                     silu_mul_f16(__float2half_rn(v[i + 2]), __float2half_rn(v[i + 3])));
+    o[i >> 2] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  if (nv == 32 && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {
+    *reinterpret_cast<uint4*>(op) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(op + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (2 * i + 1 < nv) op[i] = __ushort_as_half(static_cast<unsigned short>(o[i >> 1] >> ((i & 1) * 16)));
+  }
+}
+
 struct LinearGemmCfg {
   static constexpr int BM = 128, BN = 256, BK = 64, kStages = 4;
   static constexpr int kABytes = BM * BK * 2;  // 16 KiB
@@ -162,6 +188,8 @@ __global__ void __launch_bounds__(192, 1)
               for (int i = 0; i < 32; ++i)
                 if (i < nv) op[i] = v[i];
             }
+          } else if (g.out_dtype == kLinearOutSiluPairs) {
+            store_silu_pairs32(g, m, n, nv, v);
           } else {
             __half* op = static_cast<__half*>(g.out) + static_cast<int64_t>(m) * g.ldo + n;
             if (nv == 32 && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {

@@ -159,6 +159,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
               for (int i = 0; i < 32; ++i)
                 if (i < nv) op[i] = v[i];
             }
+          } else if (g.out_dtype == kLinearOutSiluPairs) {
+            store_silu_pairs32(g, m, n, nv, v);
           } else {
             __half* op = static_cast<__half*>(g.out) + static_cast<int64_t>(m) * g.ldo + n;
             if (nv == 32 && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {

@@ -313,3 +313,17 @@ class Context:
             None if resid is None else resid.data_ptr(), 0 if resid is None else resid.stride(0), M, N, K,
             C.byref(ms) if timed else None))
         return (out, ms.value) if timed else out
+
+    def linear_f16_silu(self, a: torch.Tensor, w_gate_up: torch.Tensor, h: torch.Tensor | None = None):
+        """h[M, N/2] = fp16(silu(gate) * up) of the merged projection whose weight rows interleave gate and up
+        (hl_b200_linear_f16_silu); M >= 16."""
+        assert a.is_cuda and w_gate_up.is_cuda and a.dtype == torch.float16 and w_gate_up.dtype == torch.float16
+        assert a.stride(1) == 1 and w_gate_up.stride(1) == 1 and a.shape[1] == w_gate_up.shape[1]
+        M, K = a.shape
+        N = w_gate_up.shape[0]
+        if h is None:
+            h = torch.empty((M, N // 2), dtype=torch.float16, device=a.device)
+        assert h.dtype == torch.float16 and h.stride(1) == 1 and h.shape == (M, N // 2)
+        self._check(self.lib.hl_b200_linear_f16_silu(self.handle, a.data_ptr(), a.stride(0), w_gate_up.data_ptr(),
+                                                     w_gate_up.stride(0), h.data_ptr(), h.stride(0), M, N, K, None))
+        return h

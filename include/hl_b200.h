@@ -244,6 +244,15 @@ int32_t hl_b200_linear_f16(hl_ctx* ctx, const void* a, int64_t lda, const void* 
                            int32_t out_dtype, int64_t ldo, const float* resid, int64_t ldr, int32_t M,
                            int32_t N, int32_t K, float* gpu_ms);
 
+/* The merged gate|up projection of a SwiGLU feed-forward block with its activation in the GEMM epilogue:
+ * W [N, K] holds the gate and up rows INTERLEAVED (row 2c = gate row c, row 2c + 1 = up row c), and
+ * h[M, N / 2] = fp16( silu(fp16 gate) * fp16 up ), silu(g) = g / (1 + expf(-g)) -- bit for bit what
+ * hl_b200_linear_f16 with fp16 output followed by the reference's siluMulKernel (naive.nim:2179-2197,
+ * call site naive.nim:4083-4085) gives, without the fp16 [M, N] intermediate.  M >= 16 (the tcgen05
+ * GEMMs; the single-token decode path fuses the same activation into its GEMV). */
+int32_t hl_b200_linear_f16_silu(hl_ctx* ctx, const void* a, int64_t lda, const void* w, int64_t ldw, void* h,
+                                int64_t ldh, int32_t M, int32_t N, int32_t K, float* gpu_ms);
+
 /* No counterpart in the reference.  Self-test of the bounded-wait machinery: launches one CTA that
  * waits, for at most `max_polls` polls, on a barrier nothing ever signals.  The wait gives up,
  * the kernel returns normally, and hl_b200_device_status then reports {HL_ERR_TIMEOUT, 900}.  The

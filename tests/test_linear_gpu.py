@@ -96,3 +96,43 @@ def test_attention_output_feeds_the_projection_in_fp16(hl_ctx):
     want = oracle.matmul(ref_attn, np.ascontiguousarray(wo.astype(np.float32).T))
     assert float(np.abs(got - want).max()) < 5e-3 and float(np.linalg.norm(got - want) / np.linalg.norm(want)) < 2e-3
     kv.destroy()
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 64, 64), (100, 300, 200), (129, 512, 128), (300, 1024, 2048), (512, 512, 256),
+                                   (640, 1100, 320), (2048, 1024, 512)])
+def test_gate_up_projection_with_silu_in_the_epilogue(hl_ctx, M, N, K):
+    """hl_b200_linear_f16_silu: h[m][c] = fp16(silu(gate) * up) with gate / up = accumulator columns 2c / 2c + 1
+    (siluMulKernel, naive.nim:2179-2197, on the output of the merged projection).  Against the oracle's matmul on
+    the fp16-rounded operands; and, where the plain projection runs the same GEMM kernel (M > 128), against the
+    two-step form built from its fp16 output: equal up to one fp16 ulp where expf differs in its last bit."""
+    g = np.random.Generator(np.random.PCG64([7, M, N, K]))
+    a = g.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+    w = (g.standard_normal((N, K), dtype=np.float32) / np.sqrt(K)).astype(np.float16)
+    a_d, w_d = torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda()
+    h = hl_ctx.linear_f16_silu(a_d, w_d)
+    assert hl_ctx.device_status() == (0, 0)
+    gu = oracle.matmul(a.astype(np.float32), np.ascontiguousarray(w.astype(np.float32).T)).astype(np.float16).astype(np.float32)
+    gate, up = gu[:, 0::2], gu[:, 1::2]
+    want = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float32)
+    got = h.float().cpu().numpy()
+    assert got.shape == (M, N // 2)
+    err = float(np.abs(got - want).max())
+    assert err < 4e-3 * max(1.0, float(np.abs(want).max())), f"M={M} N={N} K={K}: max-abs {err:.3e} vs the oracle"
+    if M > 128:
+        gu_d = hl_ctx.linear_f16(a_d, w_d, out_dtype=torch.float16).float()
+        two_step = (gu_d[:, 0::2] * torch.sigmoid(gu_d[:, 0::2]) * gu_d[:, 1::2]).half()
+        diff = (h.view(torch.int16).int() - two_step.view(torch.int16).int()).abs()
+        assert int(diff.max()) <= 1, "more than one fp16 ulp from the two-step form"
+        assert float((diff != 0).float().mean()) < 2e-2
+
+
+def test_gate_up_projection_refuses_what_it_cannot_do(hl_ctx):
+    a = torch.zeros((8, 64), dtype=torch.float16, device="cuda")
+    w = torch.zeros((64, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(hl.HlError):
+        hl_ctx.linear_f16_silu(a, w)            # fewer than 16 rows: the decode path's fused GEMV serves those
+    a = torch.zeros((32, 64), dtype=torch.float16, device="cuda")
+    w = torch.zeros((63, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(hl.HlError):
+        hl_ctx.linear_f16_silu(a, w, torch.empty((32, 31), dtype=torch.float16, device="cuda"))  # odd N
+    assert hl_ctx.device_status() == (0, 0)
