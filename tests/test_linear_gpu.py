@@ -136,3 +136,17 @@ def test_gate_up_projection_refuses_what_it_cannot_do(hl_ctx):
     with pytest.raises(hl.HlError):
         hl_ctx.linear_f16_silu(a, w, torch.empty((32, 31), dtype=torch.float16, device="cuda"))  # odd N
     assert hl_ctx.device_status() == (0, 0)
+
+
+def test_projection_reproduces_the_reference_tests_known_answers(hl_ctx, wmma_known_answers):
+    """The closed-form fp16 x fp16 -> fp32 products of the reference's tests/integration_wmma.nim (:33-60 and :70-76),
+    through hl_b200_linear_f16 (out = A . W^T): exact, every value is an integer below 2^24."""
+    for a, b, c in wmma_known_answers:
+        w = np.ascontiguousarray(b.T)                          # W[n][k] = B[k][n]
+        for rows in (16, 1):                                   # 16 rows: tcgen05 path; one row: the GEMV
+            if w.shape[0] < 1:
+                continue
+            out = hl_ctx.linear_f16(torch.from_numpy(a[:rows].astype(np.float16)).cuda(),
+                                    torch.from_numpy(w.astype(np.float16)).cuda())
+            assert np.array_equal(out.cpu().numpy(), c[:rows]), (rows, out.cpu().numpy(), c[:rows])
+    assert hl_ctx.device_status() == (0, 0)

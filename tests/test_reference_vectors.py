@@ -30,3 +30,9 @@ def test_half_bit_patterns_of_the_reference():
     assert np.isposinf(np.array([0x7C00], np.uint16).view(np.float16)[0])
     assert np.isneginf(np.array([0xFC00], np.uint16).view(np.float16)[0])
     assert np.isnan(np.array([0x7C01], np.uint16).view(np.float16)[0])
+
+
+def test_oracle_matmul_reproduces_the_wmma_known_answers(wmma_known_answers):
+    for a, b, c in wmma_known_answers:
+        assert np.array_equal(a.astype(np.float16).astype(np.float32), a)
+        assert np.array_equal(oracle.matmul(a, b), c)
