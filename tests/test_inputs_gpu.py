@@ -126,7 +126,7 @@ def test_prefill_bcast_with_fp16_inputs_against_the_oracle(hl_ctx):
     kv.destroy()
 
 
-@pytest.mark.parametrize("hd,rope_dim", [(128, 64), (64, 32), (128, 96)])
+@pytest.mark.parametrize("hd,rope_dim", [(128, 64), (64, 32), (128, 96), (128, 78)])  # 78 of 128: Nemotron-H (tests/integration_nemotron.nim:33)
 @pytest.mark.parametrize("rope_mode", [hl.HL_ROPE_INTERLEAVED, hl.HL_ROPE_SPLIT_HALF], ids=["interleaved", "split-half"])
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_partial_rotary(hl_ctx, hd, rope_dim, rope_mode, kernel):
