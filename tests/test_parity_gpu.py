@@ -36,6 +36,8 @@ def _setup(hl_ctx, n_head, n_head_kv, hd, S_total, bt, rope_mode, norm, seed, ba
     (128, 8, 1, 257, 64, hl.HL_ROPE_SPLIT_HALF, False),
     (128, 4, 2, 513, 128, hl.HL_ROPE_INTERLEAVED, False),
     (128, 4, 2, 640, 128, hl.HL_ROPE_SPLIT_HALF, True),
+    (128, 10, 2, 300, 16, hl.HL_ROPE_SPLIT_HALF, False),    # group of 5 query heads per KV head (Nemotron-H: 40 / 8)
+    (64, 14, 2, 270, 16, hl.HL_ROPE_INTERLEAVED, True),     # group of 7 (28 / 4 models)
     (64, 8, 2, 300, 16, hl.HL_ROPE_SPLIT_HALF, False),
 ])
 @pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tcgen05", "tcgen05-pair"])
@@ -70,6 +72,9 @@ def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm, k
     (128, 32, 8, 16, hl.HL_ROPE_SPLIT_HALF, True, [300, 1, 1000, 64], 64),
     (128, 8, 8, 32, hl.HL_ROPE_INTERLEAVED, False, [513, 77], 128),
     (64, 16, 1, 16, hl.HL_ROPE_SPLIT_HALF, True, [90, 200, 333], 0),
+    (128, 10, 2, 16, hl.HL_ROPE_SPLIT_HALF, False, [1, 31, 260, 700], 0),    # group of 5
+    (64, 14, 2, 16, hl.HL_ROPE_INTERLEAVED, True, [65, 500], 64),            # group of 7
+    (128, 12, 1, 16, hl.HL_ROPE_SPLIT_HALF, False, [130], 0),                # group of 12
 ])
 def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs, chunk):
     ctxs = np.asarray(ctxs, np.int32)
