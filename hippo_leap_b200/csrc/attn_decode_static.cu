@@ -135,5 +135,7 @@ extern "C" int32_t hl_b200_attn_decode_static(hl_ctx* ctx, hl_kv* kv, int32_t la
   a.block_tokens = kv->block_tokens;
   a.num_blocks = kv->num_blocks;
   a.max_blocks = max_blocks_per_seq;
+  if (s->head_dim != 64 && s->head_dim != 128)
+    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "attn_decode_static: head_dim %d (the fixed scratch is laid out for 64 and 128)", s->head_dim);
   return s->head_dim == 64 ? launch<64>(ctx, kv, layer, a, batch) : launch<128>(ctx, kv, layer, a, batch);
 }

@@ -71,8 +71,8 @@ int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int
   if (s->n_head_kv != kv->n_head_kv || s->head_dim != kv->head_dim)
     return hl_fail(ctx, HL_ERR_ARG, "shape (n_head_kv %d, head_dim %d) does not match the KV pool (%d, %d)",
                    s->n_head_kv, s->head_dim, kv->n_head_kv, kv->head_dim);
-  if (s->head_dim != 64 && s->head_dim != 128)
-    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "head_dim %d: kernels are built for 64 and 128", s->head_dim);
+  if (s->head_dim != 64 && s->head_dim != 128 && s->head_dim != 256)
+    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "head_dim %d: kernels are built for 64, 128 and 256", s->head_dim);
   if (s->rope_dim < 0 || s->rope_dim > s->head_dim || (s->rope_dim & 1))
     return hl_fail(ctx, HL_ERR_ARG, "rope_dim %d must be even and <= head_dim", s->rope_dim);
   if (s->rope_mode != HL_ROPE_INTERLEAVED && s->rope_mode != HL_ROPE_SPLIT_HALF)
@@ -313,7 +313,8 @@ extern "C" int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_he
   if (!out) return hl_fail(ctx, HL_ERR_ARG, "kv_create: null out");
   *out = nullptr;
   if (n_layers <= 0 || n_head_kv <= 0 || num_blocks <= 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: non-positive size");
-  if (head_dim != 64 && head_dim != 128) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "kv_create: head_dim must be 64 or 128");
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+    return hl_fail(ctx, HL_ERR_UNSUPPORTED, "kv_create: head_dim must be 64, 128 or 256");
   if (block_tokens <= 0 || block_tokens % 16 != 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: block_tokens must be a multiple of 16");
   const uint64_t rows = static_cast<uint64_t>(num_blocks) * n_head_kv * block_tokens;
   if (rows >= (1ull << 31)) return hl_fail(ctx, HL_ERR_CAPACITY, "kv_create: pool has too many rows for 32-bit TMA coordinates");
@@ -420,8 +421,9 @@ static int32_t launch_append(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_att
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
   // the append may overlap the tail of the kernel in front, and the attention kernel behind (decode or prefill) starts
   // its set-up and query prologue during the append
-  HL_CUDA(ctx, s->head_dim == 64 ? launch_pdl(kv_append_kernel<64>, dim3(grid), dim3(128), 0, ctx->stream, a)
-                                 : launch_pdl(kv_append_kernel<128>, dim3(grid), dim3(128), 0, ctx->stream, a));
+  HL_CUDA(ctx, s->head_dim == 64    ? launch_pdl(kv_append_kernel<64>, dim3(grid), dim3(128), 0, ctx->stream, a)
+               : s->head_dim == 128 ? launch_pdl(kv_append_kernel<128>, dim3(grid), dim3(128), 0, ctx->stream, a)
+                                    : launch_pdl(kv_append_kernel<256>, dim3(grid), dim3(128), 0, ctx->stream, a));
   ctx->launches++;
   HL_CUDA(ctx, cudaGetLastError());
   return HL_OK;
@@ -444,7 +446,7 @@ extern "C" int32_t hl_b200_kv_append_batch(hl_ctx* ctx, hl_kv* kv, int32_t layer
 // ---------------------------------------------------------------------------------------------
 template <int HD>
 static int32_t launch_decode(hl_ctx* ctx, hl_kv* kv, int32_t layer, const DecodeArgs& a, int32_t batch) {
-  constexpr int NW = 4, STAGES = HD == 128 ? 3 : 4;
+  constexpr int NW = 4, STAGES = HD == 256 ? 2 : (HD == 128 ? 3 : 4);  // 64 KiB of K and V per stage at head_dim 256
   using Cfg = DecodeCfg<HD, NW, STAGES>;
   auto kern = attn_decode_kernel<HD, NW, STAGES>;
   static bool configured[16] = {};
@@ -539,7 +541,9 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
 
   rc = hl_begin_timing(ctx, gpu_ms);
   if (rc != HL_OK) return rc;
-  rc = s->head_dim == 64 ? launch_decode<64>(ctx, kv, layer, a, batch) : launch_decode<128>(ctx, kv, layer, a, batch);
+  rc = s->head_dim == 64    ? launch_decode<64>(ctx, kv, layer, a, batch)
+       : s->head_dim == 128 ? launch_decode<128>(ctx, kv, layer, a, batch)
+                            : launch_decode<256>(ctx, kv, layer, a, batch);
   if (rc != HL_OK) return rc;
   return hl_end_timing(ctx, gpu_ms);
 }
@@ -585,7 +589,7 @@ extern "C" int32_t hl_b200_attn_decode_bcast(hl_ctx* ctx, hl_kv* kv, int32_t lay
 // ---------------------------------------------------------------------------------------------
 template <int HD>
 static int32_t launch_prefill_mma(hl_ctx* ctx, hl_kv* kv, int32_t layer, const PrefillArgs& a) {
-  constexpr int NW = 8, STAGES = 2;
+  constexpr int NW = HD == 256 ? 4 : 8, STAGES = 2;  // head_dim 256: 64 query rows per CTA (registers: 128 accumulators per thread)
   using Cfg = PrefillMmaCfg<HD, NW, STAGES>;
   auto kern = attn_prefill_mma_kernel<HD, NW, STAGES>;
   static bool configured[16] = {};
@@ -653,7 +657,9 @@ static int32_t prefill_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn
       return hl_fail(ctx, HL_ERR_UNSUPPORTED, "prefill: the tcgen05 kernel does not take this shape");
     rc = hl_launch_prefill_tc(ctx, kv, layer, a, s->head_dim, bcast, n_bcast);
   } else {
-    rc = s->head_dim == 64 ? launch_prefill_mma<64>(ctx, kv, layer, a) : launch_prefill_mma<128>(ctx, kv, layer, a);
+    rc = s->head_dim == 64    ? launch_prefill_mma<64>(ctx, kv, layer, a)
+         : s->head_dim == 128 ? launch_prefill_mma<128>(ctx, kv, layer, a)
+                              : launch_prefill_mma<256>(ctx, kv, layer, a);
   }
   if (rc != HL_OK) return rc;
   return hl_end_timing(ctx, gpu_ms);

@@ -53,7 +53,7 @@ typedef struct hl_kv hl_kv;   /* paged fp16 KV pool for all layers of one model 
 typedef struct hl_attn_shape {
   int32_t n_head;      /* query heads                                       */
   int32_t n_head_kv;   /* KV heads; n_head % n_head_kv == 0                 */
-  int32_t head_dim;    /* 64 or 128                                         */
+  int32_t head_dim;    /* 64, 128 or 256 (256: warp-MMA prefill, no static entry) */
   int32_t rope_dim;    /* even, <= head_dim; dims >= rope_dim not rotated   */
   int32_t rope_mode;   /* HL_ROPE_*                                         */
   float rms_eps;       /* eps of the QK RMSNorm (hp.rmsEps)                 */

@@ -38,12 +38,16 @@ def _setup(hl_ctx, n_head, n_head_kv, hd, S_total, bt, rope_mode, norm, seed, ba
     (128, 4, 2, 640, 128, hl.HL_ROPE_SPLIT_HALF, True),
     (128, 10, 2, 300, 16, hl.HL_ROPE_SPLIT_HALF, False),    # group of 5 query heads per KV head (Nemotron-H: 40 / 8)
     (64, 14, 2, 270, 16, hl.HL_ROPE_INTERLEAVED, True),     # group of 7 (28 / 4 models)
+    (256, 8, 1, 300, 16, hl.HL_ROPE_SPLIT_HALF, True),      # head_dim 256, 16 / 2 heads (the reference's qwen35moe
+    (256, 4, 2, 70, 32, hl.HL_ROPE_INTERLEAVED, False),     # attention layers, tests/integration_qwen36moe.nim:25-27)
     (64, 8, 2, 300, 16, hl.HL_ROPE_SPLIT_HALF, False),
 ])
 @pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tcgen05", "tcgen05-pair"])
 def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm, kernel):
     if kernel == 3 and hd != 128:
         pytest.skip("the SM-pair kernel is built for head_dim 128")
+    if kernel == 2 and hd == 256:
+        pytest.skip("head_dim 256 runs on the warp-MMA kernel (the tcgen05 kernels are built for 64 and 128)")
     g, theta, qw, kw, shape, kv, table = _setup(hl_ctx, n_head, n_head_kv, hd, S, bt, rope_mode, norm, 11)
     q = g.standard_normal((S, n_head, hd), dtype=np.float32)
     k = g.standard_normal((S, n_head_kv, hd), dtype=np.float32)
@@ -75,6 +79,8 @@ def test_prefill_parity(hl_ctx, hd, n_head, n_head_kv, S, bt, rope_mode, norm, k
     (128, 10, 2, 16, hl.HL_ROPE_SPLIT_HALF, False, [1, 31, 260, 700], 0),    # group of 5
     (64, 14, 2, 16, hl.HL_ROPE_INTERLEAVED, True, [65, 500], 64),            # group of 7
     (128, 12, 1, 16, hl.HL_ROPE_SPLIT_HALF, False, [130], 0),                # group of 12
+    (256, 16, 2, 16, hl.HL_ROPE_SPLIT_HALF, True, [1, 64, 65, 300, 1000], 0),   # head_dim 256 (qwen35moe: 16 / 2 heads)
+    (256, 4, 4, 32, hl.HL_ROPE_INTERLEAVED, False, [200, 33], 64),
 ])
 def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs, chunk):
     ctxs = np.asarray(ctxs, np.int32)
