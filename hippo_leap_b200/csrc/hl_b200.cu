@@ -502,7 +502,8 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
   a.max_chunks = (max_ctx_h + a.chunk_tokens - 1) / a.chunk_tokens;
   if (a.max_chunks > 65535) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode: too many chunks");
   if (a.max_chunks > 1) {
-    const size_t need = static_cast<size_t>(batch) * s->n_head * a.max_chunks;
+    // slots of 128 floats: one per (sequence, head, chunk) up to head_dim 128, two at head_dim 256
+    const size_t need = static_cast<size_t>(batch) * s->n_head * a.max_chunks * ((s->head_dim + 127) / 128);
     if (need > ctx->part_cap) {  // grow-only scratch, like ensureActivationBuffers (naive.nim:241-262)
       HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       if (ctx->part_o) cudaFree(ctx->part_o);

@@ -132,3 +132,32 @@ def test_decode_parity(hl_ctx, hd, n_head, n_head_kv, bt, rope_mode, norm, ctxs,
         assert np.array_equal(out_h.numpy(), got), f"host form (pinned={pin}) differs from the device form"
     hl_ctx.set_tuning(0, 0)
     kv.destroy()
+
+
+def test_decode_head_dim_256_sizes_its_own_partials_scratch():
+    """A context of its own, so that the split-KV partials scratch grows from nothing at head_dim 256 (it is sized in
+    128-float slots: sized for 128 it made the chunks of neighbouring heads overwrite each other)."""
+    ctx = hl.Context(0, torch.cuda.current_stream())
+    try:
+        hd, n_head, n_head_kv, bt, c = 256, 8, 2, 16, 700
+        g = np.random.Generator(np.random.PCG64(256))
+        theta = hl.theta_table(hd, 1e4)
+        ctx.set_rope(theta)
+        shape = hl.AttnShape(n_head, n_head_kv, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+        nb = (c + bt - 1) // bt
+        kv = ctx.kv_create(1, n_head_kv, hd, bt, nb)
+        table = torch.arange(nb, dtype=torch.int32, device="cuda")
+        k = g.standard_normal((c, n_head_kv, hd), dtype=np.float32)
+        v = g.standard_normal((c, n_head_kv, hd), dtype=np.float32)
+        q = g.standard_normal((1, n_head, hd), dtype=np.float32)
+        ctx.kv_append_seq(kv, 0, shape, torch.from_numpy(k[:-1]).cuda(), torch.from_numpy(v[:-1]).cuda(), 0, table)
+        tctx = torch.tensor([c], dtype=torch.int32, device="cuda")
+        ctx.set_tuning(64, 0)                                  # eleven chunks per (sequence, KV head)
+        ctx.kv_append_batch(kv, 0, shape, torch.from_numpy(k[-1:]).cuda(), torch.from_numpy(v[-1:]).cuda(), tctx, table.view(1, -1))
+        out = ctx.attn_decode(kv, 0, shape, torch.from_numpy(q).cuda(), tctx, c, table.view(1, -1))
+        want = oracle_seq(q, k[-1:], v[-1:], theta=theta, rope_mode=hl.HL_ROPE_SPLIT_HALF, prefix=(k[:-1], v[:-1]))
+        assert_parity(out.cpu().numpy(), want, "head_dim 256 decode, fresh scratch")
+        assert ctx.device_status() == (0, 0)
+        kv.destroy()
+    finally:
+        ctx.close()
