@@ -87,7 +87,8 @@ int32_t check_hp(const hl_dense_hparams* hp) {
   if (hp->n_vocab <= 0 || hp->n_emb <= 0 || hp->n_layer <= 0 || hp->n_ffn <= 0 || hp->n_head <= 0 || hp->n_head_kv <= 0)
     return dfail(HL_ERR_ARG, "non-positive hparam");
   if (hp->n_head % hp->n_head_kv != 0) return dfail(HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
-  if (hp->head_dim != 64 && hp->head_dim != 128) return dfail(HL_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+  if (hp->head_dim != 64 && hp->head_dim != 128 && hp->head_dim != 256)
+    return dfail(HL_ERR_UNSUPPORTED, "head_dim must be 64, 128 or 256");
   if ((hp->n_emb & 7) || (hp->n_ffn & 7)) return dfail(HL_ERR_ALIGN, "n_emb and n_ffn must be multiples of 8");
   return HL_OK;
 }

@@ -192,7 +192,8 @@ int32_t check_hp(const hl_hparams* hp) {
   if (hp->n_head <= 0 && hp->n_layer > 0) return bfail(HL_ERR_ARG, "model requires head_count or SSM parameters");
   if (hp->n_vocab <= 0 || hp->n_layer <= 0 || hp->n_head_kv <= 0) return bfail(HL_ERR_ARG, "non-positive hparam");
   if (hp->n_head % hp->n_head_kv != 0) return bfail(HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
-  if (hp->head_dim != 64 && hp->head_dim != 128) return bfail(HL_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+  if (hp->head_dim != 64 && hp->head_dim != 128 && hp->head_dim != 256)
+    return bfail(HL_ERR_UNSUPPORTED, "head_dim must be 64, 128 or 256");
   return HL_OK;
 }
 

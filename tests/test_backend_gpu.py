@@ -129,6 +129,15 @@ def test_greedy_stream_multilayer_llama3_scaled_theta_and_qk_norm():
     B.unloadModelBackend()
 
 
+def test_greedy_stream_head_dim_256_qwen35moe_attention_shape():
+    """The attention shape of the reference's qwen35moe models (tests/integration_qwen36moe.nim:25-27: 16 / 2 heads,
+    head_dim 256) through the contract: 2 layers, QK-norm, 270-token prompt, 24 steps."""
+    hp = B.HParams(nVocab=512, nLayer=2, nHead=16, nHeadKv=2, headDim=256, ropeFreqBase=1e6)
+    m, cache = _drive(hp, True, 270, 24, seed=9)
+    B.freeKvCache(cache)
+    B.unloadModelBackend()
+
+
 def test_bad_hparams_rejected_before_any_launch():
     hp = B.HParams(nVocab=64, nLayer=1, nHead=6, nHeadKv=4, headDim=64)
     with pytest.raises(ValueError, match="divisible"):
