@@ -46,6 +46,7 @@ SYMBOLS = {
     "hl_b200_theta_llama3_scale_h": (_i32, [_f32p, _i32, C.c_float, C.c_float, C.c_float, _i32]),
     "hl_b200_set_rope": (_i32, [_vp, _f32p, _i32]),
     "hl_b200_kv_create": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, C.POINTER(_vp)]),
+    "hl_b200_kv_create_layers": (_i32, [_vp, _i32, C.POINTER(_i32), _i32, _i32, _i32, _i32, C.POINTER(_vp)]),
     "hl_b200_kv_destroy": (_i32, [_vp, _vp]),
     "hl_b200_kv_layer": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(C.c_size_t)]),
     "hl_b200_kv_append_seq": (_i32, [_vp, _vp, _i32, _shape_p, _view_p, _view_p, _i32, _i32, _vp, _i32]),

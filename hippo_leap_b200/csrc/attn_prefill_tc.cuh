@@ -995,7 +995,7 @@ static int32_t hl_prefill_tc_fill_args(hl_ctx* ctx, hl_kv* kv, const hl::Prefill
     ta.cs_table = static_cast<const float2*>(ctx->cs_table);
   }
   ta.box_rows = 16;
-  ta.oob_row = static_cast<uint32_t>(static_cast<uint64_t>(kv->num_blocks) * kv->n_head_kv * kv->block_tokens);
+  ta.oob_row = static_cast<uint32_t>(static_cast<uint64_t>(kv->num_blocks) * a.n_head_kv * kv->block_tokens);  // this layer's rows
   return HL_OK;
 }
 

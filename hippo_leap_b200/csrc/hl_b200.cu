@@ -68,9 +68,9 @@ int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int
     return hl_fail(ctx, HL_ERR_ARG, "layer %d outside [0, %d)", layer, kv->n_layers);
   if (s->n_head <= 0 || s->n_head_kv <= 0 || s->n_head % s->n_head_kv != 0)
     return hl_fail(ctx, HL_ERR_ARG, "GQA requires head_count divisible by head_count_kv");
-  if (s->n_head_kv != kv->n_head_kv || s->head_dim != kv->head_dim)
-    return hl_fail(ctx, HL_ERR_ARG, "shape (n_head_kv %d, head_dim %d) does not match the KV pool (%d, %d)",
-                   s->n_head_kv, s->head_dim, kv->n_head_kv, kv->head_dim);
+  if (s->n_head_kv != kv->layer_kvh[layer] || s->head_dim != kv->head_dim)
+    return hl_fail(ctx, HL_ERR_ARG, "shape (n_head_kv %d, head_dim %d) does not match layer %d of the KV pool (%d, %d)",
+                   s->n_head_kv, s->head_dim, layer, kv->layer_kvh[layer], kv->head_dim);
   if (s->head_dim != 64 && s->head_dim != 128 && s->head_dim != 256)
     return hl_fail(ctx, HL_ERR_UNSUPPORTED, "head_dim %d: kernels are built for 64, 128 and 256", s->head_dim);
   if (s->rope_dim < 0 || s->rope_dim > s->head_dim || (s->rope_dim & 1))
@@ -309,15 +309,26 @@ static int32_t make_map(hl_ctx* ctx, CUtensorMap* map, void* pool, uint64_t rows
 
 extern "C" int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_head_kv, int32_t head_dim,
                                      int32_t block_tokens, int32_t num_blocks, hl_kv** out) {
+  return hl_b200_kv_create_layers(ctx, n_layers, nullptr, n_head_kv, head_dim, block_tokens, num_blocks, out);
+}
+
+extern "C" int32_t hl_b200_kv_create_layers(hl_ctx* ctx, int32_t n_layers, const int32_t* layer_n_head_kv,
+                                            int32_t n_head_kv, int32_t head_dim, int32_t block_tokens,
+                                            int32_t num_blocks, hl_kv** out) {
   if (!ctx) return HL_ERR_ARG;
   if (!out) return hl_fail(ctx, HL_ERR_ARG, "kv_create: null out");
   *out = nullptr;
   if (n_layers <= 0 || n_head_kv <= 0 || num_blocks <= 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: non-positive size");
+  int max_kvh = n_head_kv;
+  for (int l = 0; layer_n_head_kv && l < n_layers; ++l) {
+    if (layer_n_head_kv[l] < 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: negative KV head count at layer %d", l);
+    if (layer_n_head_kv[l] > max_kvh) max_kvh = layer_n_head_kv[l];
+  }
   if (head_dim != 64 && head_dim != 128 && head_dim != 256)
     return hl_fail(ctx, HL_ERR_UNSUPPORTED, "kv_create: head_dim must be 64, 128 or 256");
   if (block_tokens <= 0 || block_tokens % 16 != 0) return hl_fail(ctx, HL_ERR_ARG, "kv_create: block_tokens must be a multiple of 16");
-  const uint64_t rows = static_cast<uint64_t>(num_blocks) * n_head_kv * block_tokens;
-  if (rows >= (1ull << 31)) return hl_fail(ctx, HL_ERR_CAPACITY, "kv_create: pool has too many rows for 32-bit TMA coordinates");
+  if (static_cast<uint64_t>(num_blocks) * max_kvh * block_tokens >= (1ull << 31))
+    return hl_fail(ctx, HL_ERR_CAPACITY, "kv_create: pool has too many rows for 32-bit TMA coordinates");
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
   hl_kv* kv = new hl_kv();
   kv->n_layers = n_layers;
@@ -325,7 +336,9 @@ extern "C" int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_he
   kv->head_dim = head_dim;
   kv->block_tokens = block_tokens;
   kv->num_blocks = num_blocks;
-  kv->bytes_each = rows * head_dim * 2;
+  kv->bytes_each = static_cast<uint64_t>(num_blocks) * n_head_kv * block_tokens * head_dim * 2;
+  kv->layer_kvh.assign(n_layers, n_head_kv);
+  kv->layer_bytes.assign(n_layers, 0);
   kv->k.assign(n_layers, nullptr);
   kv->v.assign(n_layers, nullptr);
   kv->k_map.resize(n_layers);
@@ -333,13 +346,18 @@ extern "C" int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_he
   kv->k_map128.resize(n_layers);
   kv->v_map128.resize(n_layers);
   for (int l = 0; l < n_layers; ++l) {
+    // a layer's own KV head count where one is given and positive, the default otherwise (naive.nim:3562-3563)
+    if (layer_n_head_kv && layer_n_head_kv[l] > 0) kv->layer_kvh[l] = layer_n_head_kv[l];
+    const uint64_t rows = static_cast<uint64_t>(num_blocks) * kv->layer_kvh[l] * block_tokens;
+    const size_t bytes = rows * head_dim * 2;
+    kv->layer_bytes[l] = bytes;
     // Zero-filled so that rows of a partly filled block always hold finite values.
-    if (cudaMalloc(&kv->k[l], kv->bytes_each) != cudaSuccess || cudaMalloc(&kv->v[l], kv->bytes_each) != cudaSuccess ||
-        cudaMemsetAsync(kv->k[l], 0, kv->bytes_each, ctx->stream) != cudaSuccess ||
-        cudaMemsetAsync(kv->v[l], 0, kv->bytes_each, ctx->stream) != cudaSuccess) {
+    if (cudaMalloc(&kv->k[l], bytes) != cudaSuccess || cudaMalloc(&kv->v[l], bytes) != cudaSuccess ||
+        cudaMemsetAsync(kv->k[l], 0, bytes, ctx->stream) != cudaSuccess ||
+        cudaMemsetAsync(kv->v[l], 0, bytes, ctx->stream) != cudaSuccess) {
       cudaGetLastError();
       hl_b200_kv_destroy(ctx, kv);
-      return hl_fail(ctx, HL_ERR_CUDA, "kv_create: out of device memory at layer %d (%zu bytes per pool)", l, kv->bytes_each);
+      return hl_fail(ctx, HL_ERR_CUDA, "kv_create: out of device memory at layer %d (%zu bytes per pool)", l, bytes);
     }
     int32_t rc = make_map(ctx, &kv->k_map[l], kv->k[l], rows, head_dim, 16);
     if (rc == HL_OK) rc = make_map(ctx, &kv->v_map[l], kv->v[l], rows, head_dim, 16);
@@ -373,7 +391,7 @@ extern "C" int32_t hl_b200_kv_layer(const hl_kv* kv, int32_t layer, void** k_poo
   if (!kv || layer < 0 || layer >= kv->n_layers) return HL_ERR_ARG;
   if (k_pool) *k_pool = kv->k[layer];
   if (v_pool) *v_pool = kv->v[layer];
-  if (bytes_each) *bytes_each = kv->bytes_each;
+  if (bytes_each) *bytes_each = kv->layer_bytes[layer];
   return HL_OK;
 }
 

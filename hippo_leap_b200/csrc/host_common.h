@@ -47,7 +47,9 @@ struct hl_ctx {
 
 struct hl_kv {
   int n_layers = 0, n_head_kv = 0, head_dim = 0, block_tokens = 0, num_blocks = 0;
-  size_t bytes_each = 0;
+  size_t bytes_each = 0;                     // of a layer with n_head_kv KV heads
+  std::vector<int> layer_kvh;                // KV heads of each layer (initGpuKvCache's layerNHeadKv, naive.nim:3562-3563)
+  std::vector<size_t> layer_bytes;           // bytes of each layer's K (or V) pool
   std::vector<__half*> k, v;                 // per layer pools
   std::vector<CUtensorMap> k_map, v_map;     // 16-row x 64-column boxes, 128-byte swizzle
   std::vector<CUtensorMap> k_map128, v_map128;  // 128-row boxes when a block holds >= 128 tokens

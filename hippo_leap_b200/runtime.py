@@ -157,10 +157,17 @@ class Context:
         self._check(self.lib.hl_b200_set_rope(self.handle, th.ctypes.data_as(C.POINTER(C.c_float)),
                                               th.size))
 
-    def kv_create(self, n_layers, n_head_kv, head_dim, block_tokens, num_blocks) -> KvPool:
+    def kv_create(self, n_layers, n_head_kv, head_dim, block_tokens, num_blocks, layer_n_head_kv=None) -> KvPool:
+        """``layer_n_head_kv``: KV heads per layer (entries <= 0 take ``n_head_kv``), initGpuKvCache's layerNHeadKv."""
         h = C.c_void_p()
-        self._check(self.lib.hl_b200_kv_create(self.handle, n_layers, n_head_kv, head_dim,
-                                               block_tokens, num_blocks, C.byref(h)))
+        if layer_n_head_kv is None:
+            self._check(self.lib.hl_b200_kv_create(self.handle, n_layers, n_head_kv, head_dim,
+                                                   block_tokens, num_blocks, C.byref(h)))
+        else:
+            assert len(layer_n_head_kv) == n_layers
+            arr = (C.c_int32 * n_layers)(*[int(x) for x in layer_n_head_kv])
+            self._check(self.lib.hl_b200_kv_create_layers(self.handle, n_layers, arr, n_head_kv, head_dim,
+                                                          block_tokens, num_blocks, C.byref(h)))
         return KvPool(self, h, n_layers, n_head_kv, head_dim, block_tokens, num_blocks)
 
     def kv_append_seq(self, kv: KvPool, layer: int, shape: AttnShape, k, v, start_pos: int,

@@ -111,6 +111,14 @@ int32_t hl_b200_set_rope(hl_ctx* ctx, const float* theta_h, int32_t half);
  * (position / block_tokens) to a physical block: int32 [n_seq][max_blocks_per_seq]. */
 int32_t hl_b200_kv_create(hl_ctx* ctx, int32_t n_layers, int32_t n_head_kv, int32_t head_dim,
                           int32_t block_tokens, int32_t num_blocks, hl_kv** out);
+/* The same with a KV head count per layer, the layerNHeadKv argument of initGpuKvCache
+ * (naive.nim:3552-3567; hybrid models whose attention layers differ): layer l holds
+ * layer_n_head_kv[l] KV heads where that entry is positive, n_head_kv otherwise (the rule of
+ * naive.nim:3562-3563); a null array means n_head_kv everywhere.  Every call that names a layer
+ * checks its shape against that layer's count. */
+int32_t hl_b200_kv_create_layers(hl_ctx* ctx, int32_t n_layers, const int32_t* layer_n_head_kv,
+                                 int32_t n_head_kv, int32_t head_dim, int32_t block_tokens,
+                                 int32_t num_blocks, hl_kv** out);
 int32_t hl_b200_kv_destroy(hl_ctx* ctx, hl_kv* kv);
 /* Device pointers and size in bytes of one layer's pools (to fill GpuKvCache.k/v[layer],
  * src/hippo_leap/backend_types.nim:28-34). */

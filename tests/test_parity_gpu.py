@@ -161,3 +161,42 @@ def test_decode_head_dim_256_sizes_its_own_partials_scratch():
         kv.destroy()
     finally:
         ctx.close()
+
+
+def test_kv_pool_with_a_kv_head_count_per_layer(hl_ctx):
+    """initGpuKvCache's layerNHeadKv (naive.nim:3552-3567): three layers holding 2, 4 and (entry 0 -> the default) 2 KV
+    heads.  Each layer takes the shape with ITS count -- prefill, one decode step, both against the oracle -- and
+    refuses the others'; the layer sizes reported for the GpuTensor handles follow the counts."""
+    hd, n_head, bt, S = 128, 8, 16, 200
+    counts, given = [2, 4, 2], [2, 4, 0]
+    g = np.random.Generator(np.random.PCG64(77))
+    theta = hl.theta_table(hd, 1e4)
+    hl_ctx.set_rope(theta)
+    nb = (S + 1 + bt - 1) // bt
+    kv = hl_ctx.kv_create(3, 2, hd, bt, nb, layer_n_head_kv=given)
+    table = torch.from_numpy(g.permutation(nb).astype(np.int32)).cuda()
+    for layer, kvh in enumerate(counts):
+        assert kv.layer_ptrs(layer)[2] == nb * kvh * bt * hd * 2
+        shape = hl.AttnShape(n_head, kvh, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+        q = g.standard_normal((S + 1, n_head, hd), dtype=np.float32)
+        k = g.standard_normal((S + 1, kvh, hd), dtype=np.float32)
+        v = g.standard_normal((S + 1, kvh, hd), dtype=np.float32)
+        tq, tk, tv = (torch.from_numpy(x).cuda() for x in (q, k, v))
+        hl_ctx.kv_append_seq(kv, layer, shape, tk[:S], tv[:S], 0, table)
+        for kernel in (1, 2):
+            hl_ctx.set_tuning(0, kernel)
+            try:
+                out = hl_ctx.attn_prefill(kv, layer, shape, tq[:S], 0, table)
+            finally:
+                hl_ctx.set_tuning(0, 0)
+            assert_parity(out.cpu().numpy(), oracle_seq(q[:S], k[:S], v[:S], theta=theta, rope_mode=hl.HL_ROPE_SPLIT_HALF),
+                          f"layer {layer} ({kvh} KV heads) prefill, kernel {kernel}")
+        ctx_lens = torch.tensor([S + 1], dtype=torch.int32, device="cuda")
+        hl_ctx.kv_append_batch(kv, layer, shape, tk[S:], tv[S:], ctx_lens, table.view(1, -1))
+        dec = hl_ctx.attn_decode(kv, layer, shape, tq[S:], ctx_lens, S + 1, table.view(1, -1))
+        assert_parity(dec.cpu().numpy(), oracle_seq(q[S:], k[S:], v[S:], theta=theta, rope_mode=hl.HL_ROPE_SPLIT_HALF,
+                                                    prefix=(k[:S], v[:S])), f"layer {layer} decode")
+        wrong = hl.AttnShape(n_head, 4 if kvh == 2 else 2, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+        with pytest.raises(hl.HlError):
+            hl_ctx.attn_prefill(kv, layer, wrong, tq[:S], 0, table)
+    kv.destroy()
