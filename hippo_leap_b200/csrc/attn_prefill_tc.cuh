@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(384, 1)
   const bool q_stage = fast_prologue && ta.q_stage != 0;
   // Heads vary fastest and query blocks run from the last (most keys) to the first, so the launch order is
   // longest-first over the WHOLE grid: the short blocks of every head fill the tail.  (With query blocks fastest the
-  // last head's long blocks start last and run with most SMs idle: 0.71 ms instead of 0.51 ms at 8192 tokens.)
+  // last head's long blocks start last and run with most SMs idle: 0.71 ms instead of 0.64 ms at 8192 tokens when the order was chosen.)
   // Neighbouring CTAs are the query heads of one KV head, so they share K/V tiles in L2.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a kernel queued behind may begin its own set-up
   const int q_blk = gridDim.y - 1 - blockIdx.y;
