@@ -75,3 +75,77 @@ def test_random_shape_prefill_then_decode(hl_ctx, hd, n_head_kv, group, bt, rope
                           f"decode, chunk {chunk}")
     finally:
         kv.destroy()
+
+
+def _decode_cases(n, seed):
+    g = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for i in range(n):
+        hd = int(g.choice([64, 128, 256], p=[0.35, 0.5, 0.15]))
+        n_head_kv = int(g.choice([1, 2, 4, 8]))
+        group = int(g.choice([1, 2, 4, 5, 8, 16]))
+        bt = int(g.choice([16, 32, 128]))
+        batch = int(g.integers(1, 10))
+        hi = int(g.choice([40, 300, 1500]))
+        ctxs = [int(x) for x in g.integers(1, hi + 1, batch)]
+        chunk = int(g.choice([0, 0, 64, 128, 512]))
+        half_io = bool(g.random() < 0.4)
+        norm = bool(g.random() < 0.4)
+        out.append(pytest.param(hd, n_head_kv, group, bt, ctxs, chunk, half_io, norm, i,
+                                id=f"{i}-hd{hd}-kv{n_head_kv}x{group}-bt{bt}-b{batch}-max{max(ctxs)}-c{chunk}-{'f16' if half_io else 'f32'}"))
+    return out
+
+
+@pytest.mark.parametrize("hd,n_head_kv,group,bt,ctxs,chunk,half_io,norm,seed", _decode_cases(24, 20260102))
+def test_random_batched_decode_step(hl_ctx, hd, n_head_kv, group, bt, ctxs, chunk, half_io, norm, seed):
+    """One decode step of a ragged batch over a shuffled page pool: the new K / V rows appended at each sequence's end,
+    then attention over its whole context; float32 or fp16 activations in and out."""
+    n_head = n_head_kv * group
+    g = np.random.Generator(np.random.PCG64([seed, 7]))
+    theta = hl.theta_table(hd, 5e5)
+    hl_ctx.set_rope(theta)
+    qw = g.uniform(0.8, 1.2, hd).astype(np.float32) if norm else None
+    kw = g.uniform(0.8, 1.2, hd).astype(np.float32) if norm else None
+    mode = hl.HL_ROPE_SPLIT_HALF if seed % 2 else hl.HL_ROPE_INTERLEAVED
+    shape = hl.AttnShape(n_head, n_head_kv, hd, hd, mode, 1e-6,
+                         None if qw is None else torch.from_numpy(qw).cuda(), None if kw is None else torch.from_numpy(kw).cuda())
+    ctxs = np.asarray(ctxs, np.int32)
+    B = len(ctxs)
+    need = (ctxs + bt - 1) // bt
+    num_blocks = int(need.sum()) + 4
+    perm = g.permutation(num_blocks).astype(np.int32)
+    tables = np.full((B, int(need.max())), -1, np.int32)
+    o = 0
+    for i, n in enumerate(need):
+        tables[i, :n] = perm[o:o + n]
+        o += int(n)
+    kv = hl_ctx.kv_create(1, n_head_kv, hd, bt, num_blocks)
+    ttab = torch.from_numpy(tables).cuda()
+    dt = np.float16 if half_io else np.float32
+    # what the kernels see: activations rounded to the dtype they arrive in
+    qn = g.standard_normal((B, n_head, hd), dtype=np.float32).astype(dt)
+    kn = g.standard_normal((B, n_head_kv, hd), dtype=np.float32).astype(dt)
+    vn = g.standard_normal((B, n_head_kv, hd), dtype=np.float32).astype(dt)
+    want = np.zeros((B, n_head, hd), np.float32)
+    try:
+        for i, c in enumerate(ctxs):
+            kp = g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32)
+            vp = g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32)
+            if c > 1:
+                hl_ctx.kv_append_seq(kv, 0, shape, torch.from_numpy(kp).cuda(), torch.from_numpy(vp).cuda(), 0,
+                                     ttab[i, :need[i]].contiguous())
+            want[i] = oracle_seq(qn[i:i + 1].astype(np.float32), kn[i:i + 1].astype(np.float32), vn[i:i + 1].astype(np.float32),
+                                 theta=theta, rope_mode=mode, q_norm_w=qw, k_norm_w=kw,
+                                 prefix=(kp, vp) if c > 1 else None)[0]
+        tctx = torch.from_numpy(ctxs).cuda()
+        hl_ctx.set_tuning(chunk, 0)
+        try:
+            hl_ctx.kv_append_batch(kv, 0, shape, torch.from_numpy(kn).cuda(), torch.from_numpy(vn).cuda(), tctx, ttab)
+            out = torch.empty((B, n_head, hd), dtype=torch.float16 if half_io else torch.float32, device="cuda")
+            hl_ctx.attn_decode(kv, 0, shape, torch.from_numpy(qn).cuda(), tctx, int(ctxs.max()), ttab, out)
+        finally:
+            hl_ctx.set_tuning(0, 0)
+        tol = dict(max_abs_tol=4e-3, rel_l2_tol=2e-3) if half_io else {}
+        assert_parity(out.float().cpu().numpy(), want, "batched decode step", **tol)
+    finally:
+        kv.destroy()
