@@ -150,3 +150,24 @@ def test_projection_reproduces_the_reference_tests_known_answers(hl_ctx, wmma_kn
                                     torch.from_numpy(w.astype(np.float16)).cuda())
             assert np.array_equal(out.cpu().numpy(), c[:rows]), (rows, out.cpu().numpy(), c[:rows])
     assert hl_ctx.device_status() == (0, 0)
+
+
+def _random_gemm_cases(n, seed, budget):
+    g = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    while len(out) < n:
+        M = int(g.choice([1, 2, 3, 4, 5, 15, 16, 17, 64, 127, 128, 129, 200, 511, 512, 513, 700]))
+        N = int(g.choice([1, 8, 24, 100, 256, 257, 1000, 2048, 3072]))
+        K = int(8 * g.integers(1, 600))
+        if M * N * K > budget:
+            continue
+        out.append(pytest.param(M, N, K, bool(g.random() < 0.5), bool(g.random() < 0.4), len(out),
+                                id=f"{len(out)}-{M}x{N}x{K}"))
+    return out
+
+
+@pytest.mark.parametrize("M,N,K,resid,half_out,seed", _random_gemm_cases(30, 20260103, 6e7))
+def test_random_projection_shapes_against_oracle_matmul(hl_ctx, M, N, K, resid, half_out, seed):
+    """Ragged M / N / K across the four kernels behind hl_b200_linear_f16 (GEMV, several-row, single-SM and SM-pair
+    GEMM), with and without the residual, float32 or fp16 output."""
+    _check(hl_ctx, M, N, K, resid=resid, out_dtype=torch.float16 if half_out else torch.float32, seed=1000 + seed)
