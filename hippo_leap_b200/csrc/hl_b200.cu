@@ -162,6 +162,11 @@ extern "C" int32_t hl_b200_destroy(hl_ctx* ctx) {
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->ev2) cudaEventDestroy(ctx->ev2);
   if (ctx->ev3) cudaEventDestroy(ctx->ev3);
+  for (int i = 0; i < 3; ++i) {
+    if (ctx->side_done[i]) cudaEventDestroy(ctx->side_done[i]);
+    if (ctx->side_stream[i]) cudaStreamDestroy(ctx->side_stream[i]);
+  }
+  if (ctx->fork_ev) cudaEventDestroy(ctx->fork_ev);
   if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return HL_OK;
@@ -496,6 +501,20 @@ int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_
   return static_cast<int32_t>(chunk);
 }
 
+int32_t hl_decode_reserve(hl_ctx* ctx, size_t need) {
+  if (need <= ctx->part_cap) return HL_OK;  // grow-only scratch, like ensureActivationBuffers (naive.nim:241-262)
+  HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->part_o) cudaFree(ctx->part_o);
+  if (ctx->part_ml) cudaFree(ctx->part_ml);
+  ctx->part_o = ctx->part_ml = nullptr;
+  ctx->part_cap = 0;
+  ctx->scratch_epoch++;
+  HL_CUDA(ctx, cudaMalloc(&ctx->part_o, need * 128 * sizeof(float)));
+  HL_CUDA(ctx, cudaMalloc(&ctx->part_ml, need * 2 * sizeof(float)));
+  ctx->part_cap = need;
+  return HL_OK;
+}
+
 static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_shape* s, const hl_view* q,
                            int32_t batch, const int32_t* ctx_lens, int32_t max_ctx_h, const int32_t* block_tables,
                            int32_t max_blocks_per_seq, const hl_view* gate, const hl_view* out, float* gpu_ms,
@@ -516,22 +535,16 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
   HL_CUDA(ctx, cudaSetDevice(ctx->device));
 
   DecodeArgs a{};
-  a.chunk_tokens = hl_decode_chunk_tokens(ctx, batch, s->n_head_kv, max_ctx_h);
+  a.chunk_tokens = ctx->chunk_override > 0 ? ctx->chunk_override : hl_decode_chunk_tokens(ctx, batch, s->n_head_kv, max_ctx_h);
   a.max_chunks = (max_ctx_h + a.chunk_tokens - 1) / a.chunk_tokens;
   if (a.max_chunks > 65535) return hl_fail(ctx, HL_ERR_UNSUPPORTED, "decode: too many chunks");
   if (a.max_chunks > 1) {
     // slots of 128 floats: one per (sequence, head, chunk) up to head_dim 128, two at head_dim 256
     const size_t need = static_cast<size_t>(batch) * s->n_head * a.max_chunks * ((s->head_dim + 127) / 128);
-    if (need > ctx->part_cap) {  // grow-only scratch, like ensureActivationBuffers (naive.nim:241-262)
-      HL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-      if (ctx->part_o) cudaFree(ctx->part_o);
-      if (ctx->part_ml) cudaFree(ctx->part_ml);
-      ctx->part_o = ctx->part_ml = nullptr;
-      ctx->part_cap = 0;
-      ctx->scratch_epoch++;
-      HL_CUDA(ctx, cudaMalloc(&ctx->part_o, need * 128 * sizeof(float)));
-      HL_CUDA(ctx, cudaMalloc(&ctx->part_ml, need * 2 * sizeof(float)));
-      ctx->part_cap = need;
+    if (ctx->part_base + need > ctx->part_cap) {
+      if (ctx->part_base != 0) return hl_fail(ctx, HL_ERR_CAPACITY, "decode: scratch of a batch slice was not reserved");
+      rc = hl_decode_reserve(ctx, need);
+      if (rc != HL_OK) return rc;
     }
   }
   a.q = to_view(q);
@@ -541,8 +554,8 @@ static int32_t decode_impl(hl_ctx* ctx, hl_kv* kv, int32_t layer, const hl_attn_
   a.theta = ctx->theta_d;
   a.ctx_lens = ctx_lens;
   a.block_tables = block_tables;
-  a.part_o = ctx->part_o;
-  a.part_ml = ctx->part_ml;
+  a.part_o = ctx->part_o + ctx->part_base * 128;
+  a.part_ml = ctx->part_ml + ctx->part_base * 2;
   a.status = ctx->status_d;
   a.eps = s->rms_eps;
   a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(s->head_dim));

@@ -22,7 +22,14 @@ struct hl_ctx {
   int32_t* status_d = nullptr;  // {code, detail} written by bounded waits / bounds checks
   float* part_o = nullptr;      // split-KV partial outputs (grow-only scratch)
   float* part_ml = nullptr;     // split-KV partial (max, sum)
-  size_t part_cap = 0;          // capacity in (sequence, head, chunk) triples
+  size_t part_cap = 0;          // capacity in 128-float slots (one per (sequence, head, chunk); two at head_dim 256)
+  // Set only by hl_b200_decode_step_host while it runs slices of one batch as concurrent chains: first slot of the
+  // slice in the scratch (which it has sized for the whole batch beforehand), and the chunk length of the whole batch.
+  size_t part_base = 0;
+  int32_t chunk_override = 0;
+  cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t side_done[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t fork_ev = nullptr;
   // Bumped whenever one of the grow-only scratch buffers below is re-allocated: a captured CUDA graph that baked
   // the old address in must be captured again (the backends compare this before every replay).
   uint64_t scratch_epoch = 0;
@@ -63,6 +70,8 @@ int32_t hl_check_shape(hl_ctx* ctx, const hl_kv* kv, const hl_attn_shape* s, int
 int32_t hl_check_view(hl_ctx* ctx, const hl_view* v, const char* name);
 // Tokens per split-KV chunk of a decode launch: the tuning value, or about eight CTAs per SM within 128..1024.
 int32_t hl_decode_chunk_tokens(const hl_ctx* ctx, int32_t batch, int32_t n_head_kv, int32_t max_ctx);
+// Grows the split-KV partials scratch to `slots` 128-float slots (synchronises the context's stream if it must re-allocate).
+int32_t hl_decode_reserve(hl_ctx* ctx, size_t slots);
 
 // Decode projection (linear_gemv.cuh), 1 <= M <= 4.  mode 0: a = fp16 rows; mode 1: a = fp32 rows (lda in floats),
 // RMSNorm with norm_w fused in front.  swiglu != 0: W rows interleave gate / up, out[M][N / 2] = fp16 silu(gate) * up.

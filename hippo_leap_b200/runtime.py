@@ -256,6 +256,21 @@ class Context:
             C.byref(ms) if timed else None))
         return ms.value if timed else None
 
+    def decode_step_host_call(self, kv: KvPool, layer: int, shape: AttnShape, q_h, k_h, v_h,
+                              ctx_lens: torch.Tensor, max_ctx: int, block_tables: torch.Tensor, out_h: torch.Tensor):
+        """The same call with its arguments marshalled once: returns a function of no arguments that makes the C call
+        on the SAME buffers (a serving loop that refills fixed host buffers every step); raises like the method does."""
+        sc = shape.c()
+        args = (self.handle, kv.handle, layer, C.byref(sc), self._host_ptr(q_h), self._host_ptr(k_h), self._host_ptr(v_h),
+                q_h.shape[0], _i32_dev(ctx_lens), max_ctx, _i32_dev(block_tables), block_tables.shape[1],
+                self._host_ptr(out_h), None)
+        fn, check, keep = self.lib.hl_b200_decode_step_host, self._check, (sc, q_h, k_h, v_h, ctx_lens, block_tables, out_h)
+
+        def call():
+            check(fn(*args))
+            return keep[-1]
+        return call
+
     def attn_decode_static(self, kv: KvPool, layer: int, shape: AttnShape, q, ctx_lens: torch.Tensor,
                            max_ctx: int, block_tables: torch.Tensor, out: torch.Tensor):
         """hl_b200_attn_decode_static: the decode step with no allocation inside the library.

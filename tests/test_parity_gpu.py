@@ -200,3 +200,53 @@ def test_kv_pool_with_a_kv_head_count_per_layer(hl_ctx):
         with pytest.raises(hl.HlError):
             hl_ctx.attn_prefill(kv, layer, wrong, tq[:S], 0, table)
     kv.destroy()
+
+
+def test_host_step_in_concurrent_slices_equals_the_device_form(hl_ctx):
+    """hl_b200_decode_step_host with page-locked buffers and 40 sequences runs the batch as four concurrent chains
+    (append -> decode -> combine per slice, each on its own stream, the partials scratch shared by offset): bit for bit
+    the rows of the one-launch device form, two steps in a row."""
+    hd, n_head, n_head_kv, bt, B = 128, 16, 4, 16, 40
+    g = np.random.Generator(np.random.PCG64(4040))
+    theta = hl.theta_table(hd, 5e5)
+    hl_ctx.set_rope(theta)
+    shape = hl.AttnShape(n_head, n_head_kv, hd, hd, hl.HL_ROPE_SPLIT_HALF)
+    ctxs = g.integers(1, 900, B).astype(np.int32)
+    need = (ctxs + 2 + bt - 1) // bt
+    num_blocks = int(need.sum()) + 3
+    perm = g.permutation(num_blocks).astype(np.int32)
+    tables = np.full((B, int(need.max())), -1, np.int32)
+    o = 0
+    for i, n in enumerate(need):
+        tables[i, :n] = perm[o:o + n]
+        o += int(n)
+    ttab = torch.from_numpy(tables).cuda()
+    pools = [hl_ctx.kv_create(1, n_head_kv, hd, bt, num_blocks) for _ in range(2)]  # device form / host form
+    prev = [(g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32), g.standard_normal((c - 1, n_head_kv, hd), dtype=np.float32))
+            for c in ctxs]
+    for kv in pools:
+        for i, c in enumerate(ctxs):
+            if c > 1:
+                hl_ctx.kv_append_seq(kv, 0, shape, torch.from_numpy(prev[i][0]).cuda(), torch.from_numpy(prev[i][1]).cuda(), 0,
+                                     ttab[i, :need[i]].contiguous())
+    try:
+        for step in range(2):
+            lens = torch.from_numpy(ctxs + step).cuda()
+            q = g.standard_normal((B, n_head, hd), dtype=np.float32)
+            k = g.standard_normal((B, n_head_kv, hd), dtype=np.float32)
+            v = g.standard_normal((B, n_head_kv, hd), dtype=np.float32)
+            max_ctx = int(ctxs.max()) + step
+            hl_ctx.kv_append_batch(pools[0], 0, shape, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), lens, ttab)
+            dev = hl_ctx.attn_decode(pools[0], 0, shape, torch.from_numpy(q).cuda(), lens, max_ctx, ttab).cpu().numpy()
+            bufs = [torch.from_numpy(x).pin_memory() for x in (q, k, v)]
+            out_h = torch.full((B, n_head, hd), float("nan")).pin_memory()
+            hl_ctx.decode_step_host(pools[1], 0, shape, *bufs, lens, max_ctx, ttab, out_h)
+            assert np.array_equal(out_h.numpy(), dev), f"step {step}: host step in slices differs from the device form"
+            if step == 0:   # and the oracle, for the longest and the shortest sequence
+                for i in (int(np.argmax(ctxs)), int(np.argmin(ctxs))):
+                    want = oracle_seq(q[i:i + 1], k[i:i + 1], v[i:i + 1], theta=theta, rope_mode=hl.HL_ROPE_SPLIT_HALF,
+                                      prefix=prev[i] if ctxs[i] > 1 else None)[0]
+                    assert_parity(out_h.numpy()[i], want, f"sequence {i} (ctx {ctxs[i]})")
+    finally:
+        for kv in pools:
+            kv.destroy()
