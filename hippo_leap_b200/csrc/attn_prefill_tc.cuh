@@ -3,8 +3,11 @@
 // Replaces qkNormPrefill(Q) + ropeAtPos(Q) + attentionPrefillKernel of the reference
 // (src/hippo_leap/backends/naive.nim:2928-2971, 3006-3044, 3385-3464).
 //
-// One CTA = 256 query rows of one head, as two 128-row tiles A and B that ping-pong on the tensor
-// core: while the softmax warps of one tile work on S = Q K^T, the MMA warp runs the other tile.
+// One CTA = two 128-row tiles A and B that ping-pong on the tensor core: while the softmax warps of one tile
+// work on S = Q K^T, the MMA warp runs the other tile.  The tiles are the SAME 128 query rows of two neighbouring
+// query heads of one KV head (prompts of 768 to 16384 tokens, even group size: both tiles attend the same keys, so
+// neither idles while the other finishes), or else two consecutive 128-row blocks of one head; either way they
+// share every K / V tile.
 //   warps 0-3  softmax of tile A  (thread r owns row r: TMEM lane r, no shuffles in the softmax)
 //   warps 4-7  softmax of tile B
 //   warp  8    TMA producer: K and V blocks of 128 keys from the paged cache, 128-byte swizzle; and, for
@@ -51,6 +54,11 @@ struct PrefillTcArgs {
   // reads them from shared memory; needs contiguous, 16-byte aligned head rows (set by the launcher with the map).
   int32_t q_stage;
   int32_t early_q;  // 1: the query rows are known to be complete before this grid can start (read before the wait)
+  // 1: the two tiles of a CTA are the SAME 128 query rows of two neighbouring heads of one KV head (heads 2x and 2x + 1;
+  // the group size is even) instead of two consecutive 128-row blocks of one head.  Both tiles then attend exactly the
+  // same keys: neither waits for the other at the end (the second row block always has one key block more: ~2 us per
+  // CTA with the first tile's share of the SM idle), and they still share every K / V tile.
+  int32_t pair_heads;
 };
 
 // 3-D tiled load global -> this CTA's shared memory (no multicast), completion counted on `bar`.
@@ -361,9 +369,10 @@ __global__ void __launch_bounds__(384, 1)
   // Neighbouring CTAs are the query heads of one KV head, so they share K/V tiles in L2.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a kernel queued behind may begin its own set-up
   const int q_blk = gridDim.y - 1 - blockIdx.y;
-  const int h = blockIdx.x;
+  const int hstep = ta.pair_heads ? 1 : 0, tstep = ta.pair_heads ? 0 : 128;  // tile t: head h + hstep * t, rows from t0 + tstep * t
+  const int h = ta.pair_heads ? 2 * blockIdx.x : blockIdx.x;
   const int kvh = h / a.group;
-  const int t0 = q_blk * 256;
+  const int t0 = q_blk * (ta.pair_heads ? 128 : 256);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -389,8 +398,8 @@ __global__ void __launch_bounds__(384, 1)
   int k_end[2], n_blk[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int live = min(128, a.n_tok - (t0 + 128 * t));
-    k_end[t] = live > 0 ? a.start_pos + t0 + 128 * t + live : 0;
+    const int live = min(128, a.n_tok - (t0 + tstep * t));
+    k_end[t] = live > 0 ? a.start_pos + t0 + tstep * t + live : 0;
     n_blk[t] = (k_end[t] + 127) >> 7;
   }
   const int n_max = max(n_blk[0], n_blk[1]);
@@ -440,7 +449,8 @@ __global__ void __launch_bounds__(384, 1)
     }
     if (!ta.early_q) asm volatile("griddepcontrol.wait;" ::: "memory");  // the query rows may come from the grid in front
     if (q_stage && lane == 0) {
-      // The CTA's 256 raw query rows as ONE tiled load ({head_dim, 1 head, 256 tokens}; rows past the end of the
+      // The CTA's 256 raw query rows as ONE tiled load ({head_dim, 1 head, 256 tokens}, or {head_dim, 2 heads, 128
+      // tokens} when the tiles are two heads: the launcher builds the map with the box; rows past the end of the
       // prompt are zero-filled) into the ring stages that stay idle until the prologue is over; the softmax warps read
       // them from shared memory.  (Through registers it took 32 loads per lane, ~4 us before the arithmetic could
       // start; one bulk copy per row was slower still: the copy engine's rate is per request, not per byte.)
@@ -586,7 +596,8 @@ __global__ void __launch_bounds__(384, 1)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int t = warp >> 2;
     const int r = tid & 127;
-    const int trow = t0 + 128 * t + r;          // token index of this thread's row
+    const int trow = t0 + tstep * t + r;        // token index of this thread's row
+    const int ht = h + hstep * t;               // this tile's head
     const int pos = a.start_pos + trow;         // its position
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_sel + Cfg::kColS + t * 128;
@@ -608,14 +619,14 @@ __global__ void __launch_bounds__(384, 1)
         const int d0 = lane * VEC;
         const int last_pos = a.start_pos + a.n_tok - 1;
         const int row0 = (warp & 3) * 32;
-        const int tt0 = t0 + 128 * t + row0;
+        const int tt0 = t0 + tstep * t + row0;
         const bool inter = a.rope_mode == HL_ROPE_INTERLEAVED;
         float x[32][VEC];
         if (!q_stage) {
 #pragma unroll
           for (int u = 0; u < 32; ++u) {
             if (tt0 + u < a.n_tok) {
-              load_vec<VEC>(a.q, tt0 + u, h, d0, x[u]);
+              load_vec<VEC>(a.q, tt0 + u, ht, d0, x[u]);
             } else {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
@@ -645,11 +656,14 @@ __global__ void __launch_bounds__(384, 1)
           tc_wait(q_raw, 0, a.status, 545, abort_flag);
           const bool f16 = a.q.dtype == HL_DTYPE_F16;
           const uint32_t row_bytes = HD * (f16 ? 2u : 4u);
-          const uint32_t src0 = base + Cfg::kQRawOff + (128 * t + row0) * row_bytes + d0 * (f16 ? 2u : 4u);
+          // staged layout: [256 tokens][head_dim], or [128 tokens][2 heads][head_dim] when the tiles are two heads
+          const uint32_t row_step = ta.pair_heads ? 2u * row_bytes : row_bytes;
+          const uint32_t src0 = base + Cfg::kQRawOff + (ta.pair_heads ? (row0 * 2 + t) : (128 * t + row0)) * row_bytes +
+                                d0 * (f16 ? 2u : 4u);
 #pragma unroll
           for (int u = 0; u < 32; ++u) {
             if (tt0 + u < a.n_tok) {
-              load_vec_smem<VEC>(src0 + u * row_bytes, f16, x[u]);
+              load_vec_smem<VEC>(src0 + u * row_step, f16, x[u]);
             } else {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) x[u][e] = 0.f;
@@ -730,11 +744,11 @@ __global__ void __launch_bounds__(384, 1)
       } else {
         for (int rr = 0; rr < 32; ++rr) {
           const int row = (warp & 3) * 32 + rr;
-          const int tt = t0 + 128 * t + row;
+          const int tt = t0 + tstep * t + row;
           const bool live = tt < a.n_tok;
           if (live) {
 #pragma unroll
-            for (int d = lane; d < HD; d += 32) xrow[d] = view_load(a.q, tt, h, d);
+            for (int d = lane; d < HD; d += 32) xrow[d] = view_load(a.q, tt, ht, d);
             __syncwarp();
             norm_rope_row<HD>(xrow, a.q_norm_w, a.eps, a.theta, a.rope_dim, a.rope_mode, a.start_pos + tt, lane);
           }
@@ -765,7 +779,7 @@ __global__ void __launch_bounds__(384, 1)
       for (int q4 = 0; q4 < 4; ++q4) tc_ld32f(tS + q4 * 32, s + q4 * 32);
       tc_wait_ld();
       const int key0 = j * 128;
-      const bool diag = key0 + 127 > a.start_pos + t0 + 128 * t;  // block touches this tile's diagonal
+      const bool diag = key0 + 127 > a.start_pos + t0 + tstep * t;  // block touches this tile's diagonal
       if (diag) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
@@ -878,7 +892,7 @@ __global__ void __launch_bounds__(384, 1)
         for (int i = 0; i < 32; ++i) oreg[i] *= inv;
         if (live && a.gate.ptr != nullptr) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) oreg[i] = apply_gate(a.gate, trow, h, q4 * 32 + i, oreg[i]);
+          for (int i = 0; i < 32; ++i) oreg[i] = apply_gate(a.gate, trow, ht, q4 * 32 + i, oreg[i]);
         }
         if (staged) {
 #pragma unroll
@@ -890,7 +904,7 @@ __global__ void __launch_bounds__(384, 1)
                          : "memory");
           }
         } else if (live) {
-          const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(h) * a.out.hs + q4 * 32;
+          const int64_t off = static_cast<int64_t>(trow) * a.out.ts + static_cast<int64_t>(ht) * a.out.hs + q4 * 32;
           for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {  // destination 0 is the local output
             void* obase = dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1];
             if (a.out.ds == 1 && a.out.dtype == HL_DTYPE_F16) {
@@ -907,7 +921,7 @@ __global__ void __launch_bounds__(384, 1)
               View ov = a.out;
               ov.ptr = obase;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) view_store(ov, trow, h, q4 * 32 + i, oreg[i]);
+              for (int i = 0; i < 32; ++i) view_store(ov, trow, ht, q4 * 32 + i, oreg[i]);
             }
           }
         }
@@ -915,17 +929,17 @@ __global__ void __launch_bounds__(384, 1)
       if (staged) {
         named_bar_sync(1 + t, 128);  // the tile's 128 rows are in shared memory
         constexpr int kChunks = HD / 8;  // 16-byte chunks per row
-        const int rows_live = min(128, a.n_tok - (t0 + 128 * t));
+        const int rows_live = min(128, a.n_tok - (t0 + tstep * t));
         for (int dsti = 0; dsti <= ta.n_bcast; ++dsti) {
           __half* obase = static_cast<__half*>(dsti == 0 ? const_cast<void*>(a.out.ptr) : ta.bcast[dsti - 1]) +
-                          static_cast<int64_t>(h) * a.out.hs;
+                          static_cast<int64_t>(ht) * a.out.hs;
           for (int idx = r; idx < rows_live * kChunks; idx += 128) {
             const int row = idx / kChunks, ch = idx % kChunks;
             uint4 val;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
                          : "r"(o_tile + row * (HD * 2) + ((ch ^ (row & (kChunks - 1))) * 16)));
-            *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(t0 + 128 * t + row) * a.out.ts + ch * 8) = val;
+            *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(t0 + tstep * t + row) * a.out.ts + ch * 8) = val;
           }
         }
       }
@@ -1015,6 +1029,12 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
   if (rc != HL_OK) return rc;
   const bool wide = kv->block_tokens % 128 == 0;
   ta.box_rows = wide ? 128 : 16;
+  static const bool no_pair_heads = getenv("HL_B200_NO_PAIR_HEADS") != nullptr;  // for comparison runs
+  // Measured on 32/8, 64/8 and 16/2 heads, head_dim 64 and 128: 2-6 % faster from 1024 to 6144 tokens (8 % at 64/8 heads
+  // and 6144 tokens), even at 8192, 0.3 % slower at 32768 (the two-microsecond tail is nothing there), 0-3 % slower at
+  // 512 -- where less than half a wave of CTAs runs and the longest CTA, now with both tiles busy to its end, is the
+  // whole launch.
+  ta.pair_heads = (a.group % 2 == 0 && a.n_tok >= 768 && a.n_tok <= 16384 && !no_pair_heads) ? 1 : 0;
   CUtensorMap q_map{};
   {
     // TMA staging of the raw query rows: contiguous head rows whose every start is 16-byte aligned, described by a
@@ -1029,7 +1049,7 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
       cuuint64_t dims[3] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(a.n_head), static_cast<cuuint64_t>(a.n_tok)};
       cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.q.hs) * el, static_cast<cuuint64_t>(a.q.ts) * el};
-      cuuint32_t box[3] = {static_cast<cuuint32_t>(HD), 1, 256};
+      cuuint32_t box[3] = {static_cast<cuuint32_t>(HD), ta.pair_heads ? 2u : 1u, ta.pair_heads ? 128u : 256u};
       cuuint32_t estr[3] = {1, 1, 1};
       const CUresult r = reinterpret_cast<EncodeFn>(ctx->encode_tiled)(
           &q_map, a.q.dtype == HL_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
@@ -1039,7 +1059,7 @@ static int32_t hl_launch_prefill_tc_t(hl_ctx* ctx, hl_kv* kv, int32_t layer, con
     }
     if (!ta.q_stage) q_map = wide ? kv->k_map128[layer] : kv->k_map[layer];  // a valid map; never used by the kernel then
   }
-  dim3 grid(a.n_head, (a.n_tok + 255) / 256);
+  dim3 grid(ta.pair_heads ? a.n_head / 2 : a.n_head, ta.pair_heads ? (a.n_tok + 127) / 128 : (a.n_tok + 255) / 256);
   HL_CUDA(ctx, launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, ctx->stream,
                           wide ? kv->k_map128[layer] : kv->k_map[layer], wide ? kv->v_map128[layer] : kv->v_map[layer],
                           q_map, ta));
