@@ -13,9 +13,10 @@ from tests.helpers import assert_parity, oracle_seq
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("S", [300, 900])   # 900: the tcgen05 kernel's tiles are two heads of one KV head there
 @pytest.mark.parametrize("kernel", [1, 2], ids=["mma", "tcgen05"])
-def test_prefill_gate_from_fused_q_gate_buffer(hl_ctx, kernel):
-    H, Hkv, hd, S, bt = 8, 2, 128, 300, 16
+def test_prefill_gate_from_fused_q_gate_buffer(hl_ctx, kernel, S):
+    H, Hkv, hd, bt = 8, 2, 128, 16
     g = np.random.Generator(np.random.PCG64(21))
     fused = g.standard_normal((H * 2 * hd, S), dtype=np.float32)     # reference layout [2*qDim, S]
     k = g.standard_normal((S, Hkv, hd), dtype=np.float32)
