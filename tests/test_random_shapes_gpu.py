@@ -12,7 +12,7 @@ from tests.helpers import assert_parity, oracle_seq
 pytestmark = pytest.mark.gpu
 
 
-def _cases(n, seed):
+def _cases(n, seed, long_prompts=False):
     g = np.random.Generator(np.random.PCG64(seed))
     out = []
     for i in range(n):
@@ -25,12 +25,15 @@ def _cases(n, seed):
         norm = bool(g.random() < 0.5)
         prefix = 0 if g.random() < 0.4 else int(g.integers(1, 400))
         n_tok = int(g.integers(1, 520)) if g.random() < 0.8 else int(g.choice([1, 127, 128, 129, 255, 256, 257, 512]))
-        out.append(pytest.param(hd, n_head_kv, group, bt, rope_mode, rope_dim, norm, prefix, n_tok, i,
-                                id=f"{i}-hd{hd}-kv{n_head_kv}x{group}-bt{bt}-rd{rope_dim}-{'n' if norm else 'p'}-{prefix}+{n_tok}"))
+        if long_prompts:  # 768 tokens and more: the tcgen05 kernel puts two heads of one KV head into a CTA (even groups)
+            n_tok, prefix = int(g.integers(768, 1300)), min(prefix, 200)
+            n_head_kv, group = min(n_head_kv, 2), int(g.choice([2, 3, 4, 6, 8]))
+        out.append(pytest.param(hd, n_head_kv, group, bt, rope_mode, rope_dim, norm, prefix, n_tok, i + (1000 if long_prompts else 0),
+                                id=f"{'L' if long_prompts else ''}{i}-hd{hd}-kv{n_head_kv}x{group}-bt{bt}-rd{rope_dim}-{'n' if norm else 'p'}-{prefix}+{n_tok}"))
     return out
 
 
-@pytest.mark.parametrize("hd,n_head_kv,group,bt,rope_mode,rope_dim,norm,prefix,n_tok,seed", _cases(28, 20260101))
+@pytest.mark.parametrize("hd,n_head_kv,group,bt,rope_mode,rope_dim,norm,prefix,n_tok,seed", _cases(28, 20260101) + _cases(8, 20260104, long_prompts=True))
 def test_random_shape_prefill_then_decode(hl_ctx, hd, n_head_kv, group, bt, rope_mode, rope_dim, norm, prefix, n_tok, seed):
     n_head = n_head_kv * group
     g = np.random.Generator(np.random.PCG64([seed, 99]))
